@@ -51,7 +51,7 @@ class PagedCache:
         # device memory
         self.k_pools: List[torch.Tensor] = []
         self.v_pools: List[torch.Tensor] = []
-        self.call_group: Dict[int, tuple] = {}
+        self.call_group: Dict[object, tuple] = {}
         for gi, g in enumerate(self.groups):
             if isinstance(g.need, PagedLatent):
                 # one vector per position, shared by the heads: a single pool (there is no value pool)
@@ -67,9 +67,9 @@ class PagedCache:
                     self.v_pools.append(torch.zeros(v_shape, dtype=dtype, device=self.device))
             for j, call in enumerate(g.calls):
                 self.call_group[call] = (gi, j)
-        self.states: Dict[int, torch.Tensor] = {}
+        self.states: Dict[object, torch.Tensor] = {}
         for call in model.state_calls:
-            need: FixedState = model.call_need[call]
+            need: FixedState = model.need_at(call)
             if allocate:
                 self.states[call] = torch.zeros((config.max_requests, *need.shape), dtype=need.dtype,
                                                 device=self.device)
@@ -105,18 +105,25 @@ class PagedCache:
         device block tables (one per group, rows in the batch's request order)."""
         out: List[Optional[LayerCache]] = []
         order = self.model.spec.order
+
+        def one(need, key, writes):
+            if need is None:
+                return None
+            if isinstance(need, (PagedKV, PagedLatent)):
+                gi, j = self.call_group[key]
+                v_pool = self.v_pools[gi]
+                return LayerCache(need=need, k=self.k_pools[gi][j], v=None if v_pool is None else v_pool[j],
+                                  block_table=block_tables[gi], page_size=self.page_size, writes=writes)
+            return LayerCache(need=need, state=self.states[key], writes=writes)
+
         for i, call in enumerate(order):
             need = self.model.call_need[i]
             src = i if call.reads_cache_of is None else call.reads_cache_of
-            if need is None:
-                out.append(None)
-            elif isinstance(need, (PagedKV, PagedLatent)):
-                gi, j = self.call_group[src]
-                v_pool = self.v_pools[gi]
-                out.append(LayerCache(need=need, k=self.k_pools[gi][j], v=None if v_pool is None else v_pool[j],
-                                      block_table=block_tables[gi], page_size=self.page_size,
-                                      writes=call.reads_cache_of is None))
+            writes = call.reads_cache_of is None
+            if isinstance(need, tuple):
+                # a mixer made of several mixers: a cache per member
+                out.append(LayerCache(need=need, writes=writes,
+                                      parts=tuple(one(n, (src, k), writes) for k, n in enumerate(need))))
             else:
-                out.append(LayerCache(need=need, state=self.states[src],
-                                      writes=call.reads_cache_of is None))
+                out.append(one(need, src, writes))
         return out

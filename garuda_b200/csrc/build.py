@@ -38,7 +38,7 @@ KERNEL_LIBS: Dict[str, List[str]] = {
     "garuda_mixers": ["latent.cu", "moe.cu", "moe_grouped.cu"],
     # a residual of several streams, the recurrent delta-rule mixer, keys and values of unequal
     # widths stored with a bias: built when a model first uses them
-    "garuda_state": ["streams.cu", "delta_rule.cu"],
+    "garuda_state": ["streams.cu", "delta_rule.cu", "general_delta.cu", "sublayer.cu"],
 }
 HOST_SOURCES = ["cache_manager.cpp", "scheduler.cpp", "step_batch.cpp", "bindings.cpp"]
 

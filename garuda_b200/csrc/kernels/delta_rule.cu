@@ -50,7 +50,7 @@ delta_prepare_kernel(const float* __restrict__ proj, int P, const float* __restr
                      long long state_stride, const WT* __restrict__ a_log, const WT* __restrict__ dt_bias,
                      const int32_t* __restrict__ token_req, const int32_t* __restrict__ cu_q,
                      const int32_t* __restrict__ slots, float* __restrict__ prep, int W, int H, int G, int dim,
-                     int vdim) {
+                     int vdim, int per_head) {
   gb::pdl_launch_dependents();
   gb::pdl_wait();
   extern __shared__ float act[];        // [C]
@@ -82,9 +82,11 @@ delta_prepare_kernel(const float* __restrict__ proj, int P, const float* __restr
   const int off_v = 2 * G * dim, off_g = off_v + H * vdim, off_b = off_g + H * dim;
   for (int c = threadIdx.x; c < H * vdim; c += blockDim.x) out[off_v + c] = act[off_v + c];
   const float* a = second + (size_t)t * P2;
+  // per_head: one decay for all key channels of a head (its pre-activation and bias are per head)
   for (int c = threadIdx.x; c < H * dim; c += blockDim.x) {
     const float rate = expf(gb::to_float<WT>(a_log[c / dim]));
-    out[off_g + c] = expf(-rate * softplus(a[c] + gb::to_float<WT>(dt_bias[c])));
+    const int j = per_head ? c / dim : c;
+    out[off_g + c] = expf(-rate * softplus(a[j] + gb::to_float<WT>(dt_bias[j])));
   }
   for (int h = threadIdx.x; h < H; h += blockDim.x) out[off_b + h] = sigmoid(proj[(size_t)t * P + C + h]);
 }
@@ -240,12 +242,13 @@ delta_recurrence_kernel(const float* __restrict__ prep, int W, const int32_t* __
   }
 }
 
-// A block per token, a warp per head in turn: out[t][h] = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate).
-// gate: columns gate_off .. of `second`.
+// A block per token, a warp per head in turn: out[t][h] = o / sqrt(mean(o^2) + eps) * w * act(gate), act =
+// sigmoid or SiLU; w [vdim] shared by the heads or [H vdim]. gate: columns gate_off .. of `second`.
 template <typename WT, typename OT>
 __global__ void __launch_bounds__(128)
 delta_out_kernel(const float* __restrict__ o, const float* __restrict__ second, int P2, int gate_off,
-                 const WT* __restrict__ w, float eps, OT* __restrict__ out, int H, int vdim) {
+                 const WT* __restrict__ w, float eps, OT* __restrict__ out, int H, int vdim, int silu_gate,
+                 int w_per_head) {
   gb::pdl_launch_dependents();
   gb::pdl_wait();
   const int t = blockIdx.x;
@@ -256,8 +259,10 @@ delta_out_kernel(const float* __restrict__ o, const float* __restrict__ second, 
     float ss = 0.f;
     for (int c = lane; c < vdim; c += 32) ss = fmaf(row[c], row[c], ss);
     const float scale = 1.0f / sqrtf(gb::warp_sum(ss) / (float)vdim + eps);
+    const WT* wh = w_per_head ? w + (size_t)h * vdim : w;
     for (int c = lane; c < vdim; c += 32)
-      out[((size_t)t * H + h) * vdim + c] = gb::from_float<OT>((row[c] * scale) * gb::to_float<WT>(w[c]) * sigmoid(gate[c]));
+      out[((size_t)t * H + h) * vdim + c] =
+          gb::from_float<OT>((row[c] * scale) * gb::to_float<WT>(wh[c]) * (silu_gate ? silu(gate[c]) : sigmoid(gate[c])));
   }
 }
 
@@ -272,7 +277,7 @@ delta_decode_kernel(const float* __restrict__ proj, int P, const float* __restri
                     const WT* __restrict__ conv_w, int taps, const float* __restrict__ conv_state, long long conv_stride,
                     const WT* __restrict__ a_log, const WT* __restrict__ dt_bias, const WT* __restrict__ norm_w, float eps,
                     const int32_t* __restrict__ slots, float* __restrict__ state, long long state_stride, int H, int G,
-                    int dim, int vdim, OT* __restrict__ out) {
+                    int dim, int vdim, OT* __restrict__ out, int per_head, int gate_off, int silu_gate) {
   gb::pdl_launch_dependents();
   gb::pdl_wait();
   extern __shared__ float sm[];          // q^[dim], k^[dim], g[dim], scratch[32], o[vdim]
@@ -295,7 +300,7 @@ delta_decode_kernel(const float* __restrict__ proj, int P, const float* __restri
   for (int d = threadIdx.x; d < dim; d += blockDim.x) {
     sq[d] = conv(kvh * dim + d);
     sk[d] = conv(G * dim + kvh * dim + d);
-    const int c = h * dim + d;
+    const int c = per_head ? h : h * dim + d;
     sg[d] = expf(-expf(gb::to_float<WT>(a_log[h])) * softplus(second[(size_t)t * P2 + c] + gb::to_float<WT>(dt_bias[c])));
   }
   __syncthreads();
@@ -348,8 +353,9 @@ delta_decode_kernel(const float* __restrict__ proj, int P, const float* __restri
   for (int c = lane; c < vdim; c += 32) ss = fmaf(so[c], so[c], ss);
   const float scale = 1.0f / sqrtf(gb::warp_sum(ss) / (float)vdim + eps);
   if (active) {
-    const float gate = second[(size_t)t * P2 + H * dim + h * vdim + col];
-    out[((size_t)t * H + h) * vdim + col] = gb::from_float<OT>((o_val * scale) * gb::to_float<WT>(norm_w[col]) * sigmoid(gate));
+    const float gate = second[(size_t)t * P2 + gate_off + h * vdim + col];
+    out[((size_t)t * H + h) * vdim + col] =
+        gb::from_float<OT>((o_val * scale) * gb::to_float<WT>(norm_w[col]) * (silu_gate ? silu(gate) : sigmoid(gate)));
   }
 }
 
@@ -375,19 +381,21 @@ int check_sizes(const char* what, int H, int G, int dim, int vdim, int taps) {
 GB_EXPORT int gb_delta_prepare(const float* proj, int P, const float* second, int P2, const void* conv_w, int w_dtype,
                                int taps, const float* conv_state, long long conv_stride, const void* a_log,
                                const void* dt_bias, const int32_t* token_req, const int32_t* cu_q, const int32_t* slots,
-                               float* prep, int W, int T, int H, int G, int dim, int vdim, cudaStream_t stream) {
+                               float* prep, int W, int T, int H, int G, int dim, int vdim, int per_head,
+                               cudaStream_t stream) {
   if (T <= 0) return GB_OK;
   int rc = check_sizes("delta_prepare", H, G, dim, vdim, taps);
   if (rc != GB_OK) return rc;
   const int C = 2 * G * dim + H * vdim;
-  if (P < C + H || P2 < H * dim || W != C + H * dim + H) return gb::fail(GB_BAD_ARGUMENT, "delta_prepare: row widths");
+  if (P < C + H || P2 < (per_head ? H : H * dim) || W != C + H * dim + H)
+    return gb::fail(GB_BAD_ARGUMENT, "delta_prepare: row widths");
   const size_t smem = (size_t)C * sizeof(float);
   if (smem > 48 * 1024) return gb::fail(GB_UNSUPPORTED, "delta_prepare: %d convolved channels", C);
   return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
     return gb::check_pdl_launch(
         gb::launch_pdl(delta_prepare_kernel<WT>, dim3(T), dim3(256), smem, stream, dim3(1, 1, 1), proj, P, second, P2,
                        (const WT*)conv_w, taps, conv_state, conv_stride, (const WT*)a_log, (const WT*)dt_bias, token_req,
-                       cu_q, slots, prep, W, H, G, dim, vdim),
+                       cu_q, slots, prep, W, H, G, dim, vdim, per_head),
         "delta_prepare");
   });
 }
@@ -427,12 +435,14 @@ GB_EXPORT int gb_delta_recurrence(const float* prep, int W, const int32_t* cu_q,
 }
 
 GB_EXPORT int gb_delta_out(const float* o, const float* second, int P2, int gate_off, const void* w, int w_dtype,
-                           float eps, void* out, int out_dtype, int T, int H, int vdim, cudaStream_t stream) {
+                           float eps, void* out, int out_dtype, int T, int H, int vdim, int silu_gate, int w_per_head,
+                           cudaStream_t stream) {
   if (T <= 0) return GB_OK;
   return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
     return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
       return gb::check_pdl_launch(gb::launch_pdl(delta_out_kernel<WT, OT>, dim3(T), dim3(128), 0, stream, dim3(1, 1, 1), o,
-                                                 second, P2, gate_off, (const WT*)w, eps, (OT*)out, H, vdim),
+                                                 second, P2, gate_off, (const WT*)w, eps, (OT*)out, H, vdim, silu_gate,
+                                                 w_per_head),
                                   "delta_out");
     });
   });
@@ -443,7 +453,7 @@ GB_EXPORT int gb_delta_decode(const float* proj, int P, const float* second, int
                               int taps, const float* conv_state, long long conv_stride, const void* a_log,
                               const void* dt_bias, const void* norm_w, float eps, const int32_t* slots, float* state,
                               long long state_stride, int R, int H, int G, int dim, int vdim, void* out, int out_dtype,
-                              cudaStream_t stream) {
+                              int per_head, int gate_off, int silu_gate, cudaStream_t stream) {
   if (R <= 0) return GB_OK;
   int rc = check_sizes("delta_decode", H, G, dim, vdim, taps);
   if (rc != GB_OK) return rc;
@@ -457,7 +467,7 @@ GB_EXPORT int gb_delta_decode(const float* proj, int P, const float* second, int
             gb::launch_pdl(delta_decode_kernel<decltype(maxd)::value, WT, OT>, dim3(H, R), dim3(threads), smem, stream,
                            dim3(1, 1, 1), proj, P, second, P2, (const WT*)conv_w, taps, conv_state, conv_stride,
                            (const WT*)a_log, (const WT*)dt_bias, (const WT*)norm_w, eps, slots, state, state_stride, H, G,
-                           dim, vdim, (OT*)out),
+                           dim, vdim, (OT*)out, per_head, gate_off, silu_gate),
             "delta_decode");
       });
     });

@@ -191,15 +191,29 @@ class CudaOps:
                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "gb_delta_prepare": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p,
                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                             c_void_p],
+                             c_int, c_void_p],
         "gb_delta_conv_state": [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "gb_delta_recurrence": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p, c_void_p],
         "gb_delta_out": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int,
-                         c_void_p],
+                         c_int, c_int, c_void_p],
         "gb_delta_decode": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p,
                             c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int,
-                            c_void_p, c_int, c_void_p],
+                            c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "gb_gdelta_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float,
+                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "gb_gdelta_recurrence": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
+                                 c_void_p, c_void_p],
+        "gb_gdelta_decode": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float,
+                             c_void_p, c_float, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                             c_void_p],
+        "gb_qk_norm_rope_append": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                                   c_void_p, c_int, c_int, c_void_p],
+        "gb_gate_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "gb_unary_act": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "gb_sublayer_merge": [c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_int, c_void_p, c_void_p, c_float,
+                              c_void_p, c_void_p, c_int, c_int, c_void_p],
     }
 
     _MIXER_SIGNATURES = {
@@ -890,23 +904,29 @@ class CudaOps:
 
     # ------------------------------------------------------------------ gated delta rule with channel decay
     def delta_rule(self, ctx, proj, second, conv_w, a_log, dt_bias, norm_w, eps, state, heads, kv_heads, dim, vdim,
-                   taps, out):
+                   taps, out, decay_per_head: bool = False, gate: str = "sigmoid"):
         """The recurrent part of a delta-rule mixer for one step. ``proj [T, 2 G dim + H vdim + H]``
         (32-bit: q | k | v before their convolution, beta's logit), ``second [T, H dim + H vdim]``
         (32-bit: the decay's pre-activation, the output gate's logit), ``conv_w [2 G dim + H vdim,
         taps]``, ``state [slots, H dim vdim + (taps - 1) (2 G dim + H vdim)]`` (32-bit: S, then the
         kept last inputs of the convolution). ``out [T, H vdim]``: every head's read-out, divided by its
-        root mean square, times ``norm_w`` and the gate. Advances the state of the batch's requests."""
+        root mean square, times ``norm_w`` and the gate. Advances the state of the batch's requests.
+        ``decay_per_head``: one decay for all key channels of a head; ``second`` is then ``[T, H +
+        H vdim]`` and ``dt_bias [H]``. ``gate``: ``sigmoid`` or ``silu`` of the gate's logit. ``proj``
+        and ``second`` may be column ranges of one wider row (unit stride along a row)."""
         b = ctx.batch
         self._on_device(proj, second, conv_w, a_log, dt_bias, norm_w, state, out)
         T = proj.shape[0]
         H, G = int(heads), int(kv_heads)
         C = 2 * G * dim + H * vdim
         n_state = H * dim * vdim
-        _need(proj.dtype == torch.float32 and proj.is_contiguous() and proj.shape[1] == C + H, "delta_rule: proj")
-        _need(second.dtype == torch.float32 and second.is_contiguous() and second.shape[1] == H * dim + H * vdim,
+        n_decay = H if decay_per_head else H * dim
+        _need(gate in ("sigmoid", "silu"), "delta_rule: the gate is sigmoid or silu")
+        silu_gate = int(gate == "silu")
+        _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] == C + H, "delta_rule: proj")
+        _need(second.dtype == torch.float32 and second.stride(1) == 1 and second.shape[1] == n_decay + H * vdim,
               "delta_rule: second")
-        _need(conv_w.is_contiguous() and tuple(conv_w.shape) == (C, taps) and a_log.numel() == H and dt_bias.numel() == H * dim
+        _need(conv_w.is_contiguous() and tuple(conv_w.shape) == (C, taps) and a_log.numel() == H and dt_bias.numel() == n_decay
               and norm_w.numel() == vdim and conv_w.dtype == a_log.dtype == dt_bias.dtype == norm_w.dtype, "delta_rule: weights")
         _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == n_state + (taps - 1) * C,
               "delta_rule: state")
@@ -918,26 +938,166 @@ class CudaOps:
         if b.max_q_len == 1 and vdim <= 256:
             # single tokens: one kernel for everything but the shift of the kept inputs
             self._check(L, L.gb_delta_decode(
-                proj.data_ptr(), proj.shape[1], second.data_ptr(), second.shape[1], conv_w.data_ptr(), wt, taps, conv_state,
+                proj.data_ptr(), proj.stride(0), second.data_ptr(), second.stride(0), conv_w.data_ptr(), wt, taps, conv_state,
                 stride, a_log.data_ptr(), dt_bias.data_ptr(), norm_w.data_ptr(), float(eps), b.slots.data_ptr(),
-                state.data_ptr(), stride, T, H, G, dim, vdim, out.data_ptr(), _tag(out, "delta_rule out"), self._stream()),
-                "delta_decode")
+                state.data_ptr(), stride, T, H, G, dim, vdim, out.data_ptr(), _tag(out, "delta_rule out"),
+                int(decay_per_head), n_decay, silu_gate, self._stream()), "delta_decode")
         else:
             W = C + H * dim + H
             prep = ctx.ws.get("delta_prep", (T, W), torch.float32)
             o = ctx.ws.get("delta_o", (T, H * vdim), torch.float32)
             self._check(L, L.gb_delta_prepare(
-                proj.data_ptr(), proj.shape[1], second.data_ptr(), second.shape[1], conv_w.data_ptr(), wt, taps, conv_state,
+                proj.data_ptr(), proj.stride(0), second.data_ptr(), second.stride(0), conv_w.data_ptr(), wt, taps, conv_state,
                 stride, a_log.data_ptr(), dt_bias.data_ptr(), b.token_req.data_ptr(), b.cu_q.data_ptr(), b.slots.data_ptr(),
-                prep.data_ptr(), W, T, H, G, dim, vdim, self._stream()), "delta_prepare")
+                prep.data_ptr(), W, T, H, G, dim, vdim, int(decay_per_head), self._stream()), "delta_prepare")
             self._check(L, L.gb_delta_recurrence(
                 prep.data_ptr(), W, b.cu_q.data_ptr(), b.slots.data_ptr(), state.data_ptr(), stride, b.num_requests, H, G,
                 dim, vdim, o.data_ptr(), self._stream()), "delta_recurrence")
             self._check(L, L.gb_delta_out(
-                o.data_ptr(), second.data_ptr(), second.shape[1], H * dim, norm_w.data_ptr(), wt, float(eps), out.data_ptr(),
-                _tag(out, "delta_rule out"), T, H, vdim, self._stream()), "delta_out")
-        self._check(L, L.gb_delta_conv_state(proj.data_ptr(), proj.shape[1], conv_state, stride, b.cu_q.data_ptr(),
+                o.data_ptr(), second.data_ptr(), second.stride(0), n_decay, norm_w.data_ptr(), wt, float(eps), out.data_ptr(),
+                _tag(out, "delta_rule out"), T, H, vdim, silu_gate, 0, self._stream()), "delta_out")
+        self._check(L, L.gb_delta_conv_state(proj.data_ptr(), proj.stride(0), conv_state, stride, b.cu_q.data_ptr(),
                                              b.slots.data_ptr(), b.num_requests, C, taps, self._stream()), "delta_conv_state")
+
+    # ------------------------------------------------------------------ the generalized delta rule
+    def general_delta(self, ctx, proj, cols, zdec, w0, a0, decay_scale, norm_w, eps, state, heads, dim, vdim, out):
+        """The recurrent part of a generalized-delta-rule mixer for one step. ``proj [T, P]`` (32-bit):
+        the projected row; ``cols`` = the first columns of ``(r, k, v, removal logits, gate logits)`` in
+        it (``H dim`` wide each, ``v`` and the gate ``H vdim``). ``zdec [T, H dim]`` (32-bit): the decay's
+        pre-activation. Per head, with ``u`` the unit key: ``w = exp(-decay_scale sigmoid(zdec + w0))``,
+        ``a = sigmoid(logit + a0)``, ``S <- diag(w) S - (a u)(u^T S) + k v^T``, ``o = S^T r``.
+        ``state [slots, H dim vdim]`` (32-bit). ``out [T, H vdim]``: every head's read-out divided by
+        its root mean square, times ``norm_w [H vdim]`` and the sigmoid of the gate. Advances the state
+        of the batch's requests."""
+        b = ctx.batch
+        self._on_device(proj, zdec, w0, a0, norm_w, state, out)
+        T, H = proj.shape[0], int(heads)
+        HD, HV = H * dim, H * vdim
+        col_r, col_k, col_v, col_a, col_g = (int(c) for c in cols)
+        _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and zdec.dtype == torch.float32 and zdec.stride(1) == 1
+              and zdec.shape[1] >= HD, "general_delta: float32 rows")
+        _need(max(col_r + HD, col_k + HD, col_v + HV, col_a + HD, col_g + HV) <= proj.shape[1], "general_delta: columns")
+        _need(all(t.dtype == torch.float32 and t.is_contiguous() for t in (w0, a0, norm_w)) and w0.numel() == HD
+              and a0.numel() == HD and norm_w.numel() == HV, "general_delta: float32 vectors")
+        _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == HD * vdim, "general_delta: state")
+        _need(out.is_contiguous() and tuple(out.shape) == (T, HV), "general_delta: out")
+        L = self.state_lib
+        stride = state.shape[1]
+        if b.max_q_len == 1 and vdim <= 256:
+            self._check(L, L.gb_gdelta_decode(
+                proj.data_ptr(), proj.stride(0), col_r, col_k, col_v, col_a, col_g, zdec.data_ptr(), zdec.stride(0),
+                w0.data_ptr(), a0.data_ptr(), float(decay_scale), norm_w.data_ptr(), float(eps), b.slots.data_ptr(),
+                state.data_ptr(), stride, T, H, dim, vdim, out.data_ptr(), _tag(out, "general_delta out"), self._stream()),
+                "gdelta_decode")
+            return
+        W = 5 * HD + HV
+        prep = ctx.ws.get("gdelta_prep", (T, W), torch.float32)
+        o = ctx.ws.get("gdelta_o", (T, HV), torch.float32)
+        self._check(L, L.gb_gdelta_prepare(
+            proj.data_ptr(), proj.stride(0), col_r, col_k, col_v, col_a, zdec.data_ptr(), zdec.stride(0), w0.data_ptr(),
+            a0.data_ptr(), float(decay_scale), prep.data_ptr(), W, T, H, dim, vdim, self._stream()), "gdelta_prepare")
+        self._check(L, L.gb_gdelta_recurrence(
+            prep.data_ptr(), W, b.cu_q.data_ptr(), b.slots.data_ptr(), state.data_ptr(), stride, b.num_requests, H, dim,
+            vdim, o.data_ptr(), self._stream()), "gdelta_recurrence")
+        gate = proj[:, col_g:col_g + HV]
+        self._check(L, L.gb_delta_out(
+            o.data_ptr(), gate.data_ptr(), proj.stride(0), 0, norm_w.data_ptr(), GB_F32, float(eps), out.data_ptr(),
+            _tag(out, "general_delta out"), T, H, vdim, 0, 1, self._stream()), "delta_out")
+
+    # ------------------------------------------------------------------ normed queries and keys; sublayers normed behind
+    def qk_norm_rope_append(self, src, cols, q_out, k_pool, v_pool, positions, token_req, block_table, heads, kv_heads,
+                            dim, vdim, q_weight, k_weight, eps, rotary, page_size):
+        """From a projected 32-bit row ``src [T, P]`` with ``cols = (q, k, v)`` the first columns of
+        queries (``heads dim``), keys (``kv_heads dim``) and values (``kv_heads vdim``; the keys' own
+        columns where the values are the keys as projected): queries and keys are divided by their root
+        mean square per head (``q_weight [heads, dim]``, ``k_weight [dim]``, 32-bit; None: no norm),
+        then rotated (``rotary``: a ``RotaryParams`` over ``dim``, or None); queries go to ``q_out
+        [T, heads, dim]``, keys and the untouched values into their pages."""
+        self._on_device(src, q_out, k_pool, v_pool, positions, token_req, block_table, q_weight, k_weight)
+        T = src.shape[0]
+        cq, ck, cv = (int(c) for c in cols)
+        _need(src.dtype == torch.float32 and src.stride(1) == 1, "qk_norm_rope_append: a float32 row")
+        _need(max(cq + heads * dim, ck + kv_heads * dim, cv + kv_heads * vdim) <= src.shape[1], "qk_norm_rope_append: columns")
+        _need(q_out.is_contiguous() and tuple(q_out.shape) == (T, heads, dim), "qk_norm_rope_append: q_out shape")
+        _need(k_pool.dtype == q_out.dtype == v_pool.dtype and k_pool.is_contiguous() and v_pool.is_contiguous()
+              and tuple(k_pool.shape[1:]) == (kv_heads, page_size, dim)
+              and tuple(v_pool.shape[1:]) == (kv_heads, page_size, vdim), "qk_norm_rope_append: pool shapes")
+        _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and positions.dtype == torch.int32
+              and token_req.dtype == torch.int32, "qk_norm_rope_append: int32 indices")
+        _need(q_weight is None or (q_weight.dtype == torch.float32 and q_weight.is_contiguous()
+                                   and q_weight.numel() == heads * dim), "qk_norm_rope_append: q_weight float32 [heads, dim]")
+        _need(k_weight is None or (k_weight.dtype == torch.float32 and k_weight.is_contiguous()
+                                   and k_weight.numel() == dim), "qk_norm_rope_append: k_weight float32 [dim]")
+        inv, inter = None, 0
+        if rotary is not None:
+            _need(rotary.head_dim == dim, "qk_norm_rope_append: rotary is for another head width")
+            inv, inter = self.inv_freq(rotary), int(rotary.interleaved)
+        L = self.state_lib
+        self._check(L, L.gb_qk_norm_rope_append(
+            src.data_ptr(), src.stride(0), cq, ck, cv, q_out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+            _tag(q_out, "q_out"), positions.data_ptr(), token_req.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+            T, heads, kv_heads, dim, vdim, _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(inv), inter, page_size,
+            self._stream()), "qk_norm_rope_append")
+
+    UNARY_ACTS = {"sigmoid": 0, "silu": 1, "relu2": 2, "tanh": 3}
+
+    def gate_mul(self, x, gate, kind: str = "sigmoid"):
+        """``x <- x * act(gate)`` in place; ``gate [T, n]`` 32-bit logits (a column range of a wider
+        row will do), ``act`` = ``sigmoid`` or ``silu``."""
+        self._on_device(x, gate)
+        T, n = x.shape
+        _need(x.is_contiguous() and gate.dtype == torch.float32 and tuple(gate.shape) == (T, n) and gate.stride(1) == 1,
+              "gate_mul: x contiguous, gate float32 of its shape")
+        _need(kind in ("sigmoid", "silu"), "gate_mul: sigmoid or silu")
+        L = self.state_lib
+        self._check(L, L.gb_gate_mul(x.data_ptr(), _tag(x, "gate_mul x"), gate.data_ptr(), gate.stride(0), T, n,
+                                     self.UNARY_ACTS[kind], self._stream()), "gate_mul")
+
+    def activation(self, z, out, kind: str):
+        """``out = act(z)`` elementwise, 32-bit arithmetic; ``act`` = ``relu2`` (the square of
+        relu), ``tanh``, ``sigmoid`` or ``silu``. Both may be column ranges of wider rows."""
+        self._on_device(z, out)
+        T, n = z.shape
+        _need(tuple(out.shape) == (T, n) and z.stride(1) == 1 and out.stride(1) == 1, "activation: shapes")
+        _need(kind in self.UNARY_ACTS, f"activation: unknown kind {kind!r}")
+        L = self.state_lib
+        self._check(L, L.gb_unary_act(z.data_ptr(), _tag(z, "activation in"), z.stride(0), out.data_ptr(),
+                                      _tag(out, "activation out"), out.stride(0), T, n, self.UNARY_ACTS[kind],
+                                      self._stream()), "activation")
+
+    def sublayer_merge(self, ys, branch_weights, eps, x=None, out=None, gate=None, gate_bias=None, weight=None,
+                       branch_eps=None):
+        """What stands between a sublayer's output and the residual where the output, not the input, is
+        normed. ``ys``: one 32-bit ``[T, d]`` output, or several branches' with ``branch_weights`` (32-bit
+        ``[d]`` each): ``y = mean_b rms(y_b) * w_b``. ``gate`` (32-bit logits ``[T, d]``, a column range
+        will do) and ``gate_bias [d]``: ``y <- y * sigmoid(gate + gate_bias)``. Then ``x += rms(y) *
+        weight`` (``x`` the 32-bit residual), or with ``out`` in place of ``x``: ``out = y``. One pass."""
+        ys = list(ys)
+        self._on_device(*ys, x, out, gate, gate_bias, weight)
+        T, d = ys[0].shape
+        _need(all(y.dtype == torch.float32 and y.is_contiguous() and tuple(y.shape) == (T, d) for y in ys),
+              "sublayer_merge: float32 [T, d] outputs")
+        ws = None
+        if branch_weights is not None:
+            ws = list(branch_weights)
+            _need(len(ws) == len(ys) and all(w.dtype == torch.float32 and w.is_contiguous() and w.numel() == d for w in ws),
+                  "sublayer_merge: one float32 [d] weight per branch")
+        _need(gate is None or (gate.dtype == torch.float32 and tuple(gate.shape) == (T, d) and gate.stride(1) == 1),
+              "sublayer_merge: gate float32 [T, d]")
+        _need(gate_bias is None or (gate_bias.dtype == torch.float32 and gate_bias.numel() == d), "sublayer_merge: gate_bias")
+        target = x if x is not None else out
+        _need(target is not None and target.dtype == torch.float32 and target.is_contiguous() and tuple(target.shape) == (T, d),
+              "sublayer_merge: x or out float32 [T, d]")
+        _need(x is None or (weight is not None and weight.dtype == torch.float32 and weight.numel() == d),
+              "sublayer_merge: the norm's float32 weight")
+        n = len(ys)
+        y_ptrs = (c_void_p * n)(*[y.data_ptr() for y in ys])
+        w_ptrs = (c_void_p * n)(*[w.data_ptr() for w in ws]) if ws is not None else None
+        L = self.state_lib
+        self._check(L, L.gb_sublayer_merge(
+            y_ptrs, w_ptrs, n, 1.0 / n, float(eps if branch_eps is None else branch_eps), _ptr(gate),
+            gate.stride(0) if gate is not None else 0, _ptr(gate_bias), _ptr(weight), float(eps), _ptr(x),
+            None if x is not None else out.data_ptr(), T, d, self._stream()), "sublayer_merge")
 
     # ------------------------------------------------------------------ sampling
     def argmax(self, logits, out):

@@ -69,7 +69,7 @@ class CacheGroup:
     """Calls of the run order whose caches have the same needs and therefore
     share a pool of pages and a block table."""
     need: object                         # PagedKV
-    calls: Tuple[int, ...]               # indices into ModelSpec.order (calls that write)
+    calls: Tuple[object, ...]            # cache keys: indices into ModelSpec.order (calls that write), or (index, member)
 
 
 class Decoder:
@@ -92,18 +92,30 @@ class Decoder:
                 if self.call_need[src] != need:
                     raise ValueError(f"run order entry {i} reads a cache of another shape: {self.call_need[src]} vs {need}")
             self.call_need.append(need)
-        groups: Dict[object, List[int]] = {}
-        self.state_calls: List[int] = []
+        # A cache key is the index of a run-order entry, or (index, member) for a mixer that is made
+        # of several mixers with a cache or a state each.
+        groups: Dict[object, List[object]] = {}
+        self.state_calls: List[object] = []
         for i, (call, need) in enumerate(zip(spec.order, self.call_need)):
             if call.reads_cache_of is not None or need is None:
                 continue
-            if isinstance(need, (PagedKV, PagedLatent)):
-                groups.setdefault(need, []).append(i)
-            elif isinstance(need, FixedState):
-                self.state_calls.append(i)
-            else:
-                raise TypeError(f"unknown cache need {need!r}")
+            members = [(i, need)] if not isinstance(need, tuple) else [((i, k), n) for k, n in enumerate(need)]
+            for key, n in members:
+                if n is None:
+                    continue
+                if isinstance(n, (PagedKV, PagedLatent)):
+                    groups.setdefault(n, []).append(key)
+                elif isinstance(n, FixedState):
+                    self.state_calls.append(key)
+                else:
+                    raise TypeError(f"unknown cache need {n!r}")
         self.cache_groups = [CacheGroup(need, tuple(calls)) for need, calls in groups.items()]
+
+    def need_at(self, key):
+        """The cache need behind a cache key: of a run-order entry, or of one member of its mixer."""
+        if isinstance(key, tuple):
+            return self.call_need[key[0]][key[1]]
+        return self.call_need[key]
 
     @property
     def graph_safe(self) -> bool:

@@ -191,3 +191,117 @@ class CappedSinkAttention(Mixer):
         y = ws.get("mixer_out", (T, self.width), torch.float32)
         ops.linear(out, self.w_o, y)
         return y
+
+
+@register_mixer("normed_key_attention")
+class NormedKeyAttention(Mixer):
+    """Grouped-query attention over the paged cache whose queries and keys are RMS-normed per head
+    before they are rotated, whose values may be the keys as projected, with a temperature per
+    head and a gate on the concatenated heads. With ``h`` the mixer's input, query head ``n``
+    reading key/value head ``n // (heads / kv_heads)``:
+
+        q, k = W_q h, W_k h;   v = k (as projected; ``values="keys"``) or W_v h (``"projected"``)
+        q <- rms(q) * w_q, k <- rms(k) * w_k     per head, over ``dim`` (``qk_norm``)
+        q, k rotated at their positions: channel 2i with 2i+1, the first ``rot_dims`` channels, angle
+             position * rot_base^(-2i / rot_dims)    (``rot_base`` None: not rotated)
+        s_ij = (q_i . k_j) * scale * temp_n;   i reads j  iff  0 <= i - j < window  (None: j <= i)
+        out = W_o (concat_n softmax(s) v * sigmoid(W_g h))       (``gate``)
+
+    The temperature multiplies the query's norm weight when the weights are loaded (the rotation
+    is linear), so the attention kernel sees one scale. One product makes ``[q | k | (v) | gate]``
+    in 32-bit; one kernel norms, rotates and stores. ``names``: the tensors' local names."""
+    graph_safe = True
+
+    def __init__(self, width: int, heads: int, kv_heads: int, dim: int, scale: Optional[float] = None,
+                 window: Optional[int] = None, rot_base: Optional[float] = None, rot_dims: int = 0,
+                 rot_layout: str = "interleaved", qk_norm: bool = True, eps: float = 1e-6, temperature: bool = True,
+                 values: str = "keys", vdim: Optional[int] = None, gate: bool = True, names: Optional[dict] = None,
+                 init_std: float = 0.02):
+        if heads % kv_heads:
+            raise ValueError(f"{heads} query heads are not a multiple of {kv_heads} kv heads")
+        if values not in ("keys", "projected"):
+            raise ValueError(f"values are 'keys' or 'projected', got {values!r}")
+        if temperature and not qk_norm:
+            raise ValueError("a temperature per head goes with normed queries (it is folded into their norm's weight)")
+        self.width, self.heads, self.kv_heads, self.dim = int(width), int(heads), int(kv_heads), int(dim)
+        self.vdim = self.dim if values == "keys" or not vdim else int(vdim)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.dim)
+        self.window = int(window) if window else None
+        self.qk_norm, self.eps, self.temperature = bool(qk_norm), float(eps), bool(temperature)
+        self.values, self.gate = values, bool(gate)
+        self.names = dict({"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "q_norm": "q.norm", "k_norm": "k.norm",
+                           "temp": "temp"}, **(names or {}))
+        self.init_std = float(init_std)
+        self.rotary = None
+        if rot_base is not None and rot_dims:
+            from .rotary import Rotary
+            # frequencies in 64-bit, rounded once; channels beyond the rotated width get frequency zero
+            freqs = [float(rot_base) ** (-2.0 * i / int(rot_dims)) for i in range(int(rot_dims) // 2)]
+            self.rotary = Rotary(float(rot_base), self.dim, layout=rot_layout, inv_freq=freqs, rotary_dim=int(rot_dims)).rotary
+            if self.rotary is None:
+                raise ValueError("a rotation narrower than the head takes the interleaved pairing here")
+        self.q_dim, self.k_dim, self.v_dim = self.heads * self.dim, self.kv_heads * self.dim, self.kv_heads * self.vdim
+        self.ctx_dim = self.heads * self.vdim
+
+    def tensors(self):
+        init, n = ("normal", self.init_std), self.names
+        t = {n["q"]: TensorSpec((self.q_dim, self.width), init=init), n["k"]: TensorSpec((self.k_dim, self.width), init=init),
+             n["o"]: TensorSpec((self.width, self.ctx_dim), init=init)}
+        if self.values == "projected":
+            t[n["v"]] = TensorSpec((self.v_dim, self.width), init=init)
+        if self.gate:
+            t[n["g"]] = TensorSpec((self.ctx_dim, self.width), init=init)
+        if self.qk_norm:
+            t[n["q_norm"]] = TensorSpec((self.dim,), role="vector", init=("normal_about_one", 0.1))
+            t[n["k_norm"]] = TensorSpec((self.dim,), role="vector", init=("normal_about_one", 0.1))
+        if self.temperature:
+            t[n["temp"]] = TensorSpec((self.heads,), role="vector", init=("normal_about_one", 0.2))
+        return t
+
+    def cache_need(self):
+        return PagedKV(self.kv_heads, self.dim, self.window, value_dim=self.vdim)
+
+    def load(self, tensors, ops, dtype):
+        super().load(tensors, ops, dtype)
+        n = self.names
+        rows = [tensors[n["q"]], tensors[n["k"]]]
+        self.col_q, self.col_k = 0, self.q_dim
+        self.col_v = self.col_k
+        at = self.q_dim + self.k_dim
+        if self.values == "projected":
+            rows.append(tensors[n["v"]])
+            self.col_v, at = at, at + self.v_dim
+        self.col_g = at
+        if self.gate:
+            rows.append(tensors[n["g"]])
+        self.w_in = torch.cat(rows, dim=0).contiguous()
+        self.w_o = tensors[n["o"]].contiguous()
+        self.k_weight = tensors[n["k_norm"]].float().contiguous() if self.qk_norm else None
+        self.q_weight = None
+        if self.qk_norm:
+            per_head = tensors[n["q_norm"]].float()[None, :].expand(self.heads, self.dim)
+            if self.temperature:
+                per_head = per_head * tensors[n["temp"]].float()[:, None]
+            self.q_weight = per_head.contiguous()
+
+    def forward(self, ctx, h, cache, residual=None, out_name: str = "attn_y"):
+        b, ops, ws = ctx.batch, self.ops, ctx.ws
+        T = h.shape[0]
+        proj = ws.get("attn_proj", (T, self.w_in.shape[0]), torch.float32)
+        ops.linear(h, self.w_in, proj)
+        q = ws.get("q_heads", (T, self.heads, self.dim), self.dtype)
+        ops.qk_norm_rope_append(proj, (self.col_q, self.col_k, self.col_v), q, cache.k, cache.v, b.positions, b.token_req,
+                                cache.block_table, self.heads, self.kv_heads, self.dim, self.vdim, self.q_weight,
+                                self.k_weight, self.eps, self.rotary, cache.page_size)
+        out = ws.get("attn_ctx", (T, self.ctx_dim), self.dtype)
+        ops.paged_attention(q, cache.k, cache.v, cache.block_table, b.cu_q, b.kv_lens, b.token_req, out,
+                            self.scale, self.window or 0, cache.page_size, b.num_requests, b.max_q_len, b.max_kv_len,
+                            ws=ws, min_q_len=b.min_q_len)
+        if self.gate:
+            ops.gate_mul(out, proj[:, self.col_g:self.col_g + self.ctx_dim], "sigmoid")
+        if residual is not None:
+            ops.linear(out, self.w_o, residual, accumulate=True)
+            return None
+        y = ws.get(out_name, (T, self.width), torch.float32)
+        ops.linear(out, self.w_o, y)
+        return y

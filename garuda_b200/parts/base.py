@@ -88,7 +88,8 @@ class LayerCache:
     group's table for the requests of the batch, ``[R, max_pages]`` int32 (-1
     where a page has been given back). ``writes`` is False for a call that reads
     another call's cache. For ``FixedState``: ``state`` is ``[max_slots, *shape]``
-    and the batch's ``slots`` index it.
+    and the batch's ``slots`` index it. For a mixer made of several mixers (its ``cache_need()``
+    is a tuple): ``parts`` holds one ``LayerCache`` (or None) per entry of the tuple.
     """
     need: object
     k: Optional[torch.Tensor] = None
@@ -97,6 +98,7 @@ class LayerCache:
     page_size: int = 0
     state: Optional[torch.Tensor] = None
     writes: bool = True
+    parts: Optional[tuple] = None
 
 
 # --------------------------------------------------------------------------
@@ -148,7 +150,9 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     def cache_need(self):
-        """``PagedKV``, ``FixedState`` or ``None``."""
+        """``PagedKV``, ``PagedLatent``, ``FixedState`` or ``None``; a mixer that is made of several
+        mixers gives a tuple with one of these per member, and gets a ``LayerCache`` whose ``parts``
+        are the members' caches in that order."""
         return None
 
     def forward(self, ctx, h: torch.Tensor, cache: Optional[LayerCache],
@@ -177,6 +181,16 @@ class Connection(Part):
         raise NotImplementedError
 
 
+class SublayerGate(Part):
+    """A gate on a sublayer's output, computed from the sublayer's input: ``logits(ctx, h)`` gives
+    32-bit ``[T, d]`` logits (without the bias, which ``bias`` holds, 32-bit ``[d]`` or None); the
+    block multiplies the sublayer's output by their sigmoid."""
+    bias = None
+
+    def logits(self, ctx, h: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
 class ResidualBranch(Part):
     """Something a layer adds to the residual stream after its mixer and feed-forward, computed
     from the stream itself and the step's tokens (a per-layer token embedding, gated): it reads
@@ -193,7 +207,7 @@ class ResidualBranch(Part):
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {
     "mixer": {}, "feed_forward": {}, "norm": {}, "position_encoding": {}, "block": {}, "branch": {},
-    "connection": {},
+    "connection": {}, "gate": {},
 }
 
 
@@ -211,6 +225,7 @@ def register_position_encoding(name, cls=None): return _register("position_encod
 def register_block(name, cls=None): return _register("block", name, cls)
 def register_branch(name, cls=None): return _register("branch", name, cls)
 def register_connection(name, cls=None): return _register("connection", name, cls)
+def register_gate(name, cls=None): return _register("gate", name, cls)
 
 
 @dataclass(frozen=True)

@@ -14,7 +14,9 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
-from .base import PartSpec, build_part, register_block
+import torch
+
+from .base import PartSpec, SublayerGate, TensorSpec, build_part, register_block, register_gate
 
 
 @dataclass(frozen=True)
@@ -30,6 +32,9 @@ class BlockSpec:
     # for an arrangement over a residual of several streams: how each sublayer is joined to them
     mixer_connection: Optional[PartSpec] = None
     feed_forward_connection: Optional[PartSpec] = None
+    # for the arrangement that norms a sublayer's output: a gate on that output, per sublayer
+    mixer_gate: Optional[PartSpec] = None
+    feed_forward_gate: Optional[PartSpec] = None
 
 
 @register_block("pre_norm")
@@ -134,4 +139,110 @@ class PreNormBlock:
         for branch in self.branches:
             branch.forward(ctx, x, self.mult)
         ctx.pending_norm = None
+        return None
+
+
+@register_gate("linear_sigmoid")
+class LinearSigmoidGate(SublayerGate):
+    """``sigmoid(W h + b)``, one gate per channel of the model's width. ``weight_name``: the local
+    name of ``W [d, d]``; the bias is that name with ``.b`` added (``bias=False``: none)."""
+    graph_safe = True
+
+    def __init__(self, width: int, weight_name: str = "gate", bias: bool = True, init_std: float = 0.02):
+        self.width, self.weight_name, self.has_bias, self.init_std = int(width), weight_name, bool(bias), float(init_std)
+
+    def tensors(self):
+        t = {self.weight_name: TensorSpec((self.width, self.width), init=("normal", self.init_std))}
+        if self.has_bias:
+            t[self.weight_name + ".b"] = TensorSpec((self.width,), role="vector", init=("normal", 0.5))
+        return t
+
+    def load(self, tensors, ops, dtype):
+        super().load(tensors, ops, dtype)
+        self.weight = tensors[self.weight_name].contiguous()
+        self.bias = tensors[self.weight_name + ".b"].float().contiguous() if self.has_bias else None
+
+    def logits(self, ctx, h, name="gate_logits"):
+        out = ctx.ws.get(name, (h.shape[0], self.width), torch.float32)
+        self.ops.linear(h, self.weight, out)
+        return out
+
+
+class BranchOutputs:
+    """What a mixer made of several mixers hands to a block that norms sublayer outputs: the
+    members' 32-bit outputs ``ys`` with a weight each; the mixer's output is the mean over the
+    members of ``rms(y_b) * w_b``, which the block's one pass over the row computes."""
+
+    def __init__(self, ys, weights, eps):
+        self.ys, self.weights, self.eps = list(ys), list(weights), float(eps)
+
+    def materialize(self, ctx, name="branches_out"):
+        T, d = self.ys[0].shape
+        out = ctx.ws.get(name, (T, d), torch.float32)
+        ctx.ops.sublayer_merge(self.ys, self.weights, self.eps, out=out)
+        return out
+
+
+@register_block("sublayer_norm")
+class SublayerNormBlock:
+    """A layer whose sublayers read the residual itself and whose outputs are normed:
+    ``x += norm1(gate1 * mixer(x)); x += norm2(gate2 * ffn(x))``, with ``gate = sigmoid(W x + b)``
+    per channel from the sublayer's own input (``BlockSpec.mixer_gate`` / ``feed_forward_gate``;
+    None: no gate). The residual is 32-bit; a sublayer's input is the residual rounded to the
+    compute dtype (the residual itself in 32-bit runs); its output stays 32-bit through the gate,
+    the norm and the sum, which are one pass over the row."""
+
+    def __init__(self, spec: BlockSpec):
+        if spec.residual_mult != 1.0 or spec.branches or spec.mixer_connection is not None:
+            raise ValueError("a layer that norms its sublayers' outputs takes no multiplier, branches or streams")
+        self.spec = spec
+        self.mixer = build_part("mixer", spec.mixer)
+        self.mixer_norm = build_part("norm", spec.mixer_norm)
+        self.mixer_gate = build_part("gate", spec.mixer_gate) if spec.mixer_gate else None
+        self.feed_forward = build_part("feed_forward", spec.feed_forward) if spec.feed_forward else None
+        self.feed_forward_norm = build_part("norm", spec.feed_forward_norm) if spec.feed_forward else None
+        self.feed_forward_gate = (build_part("gate", spec.feed_forward_gate)
+                                  if spec.feed_forward and spec.feed_forward_gate else None)
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if norm is not None and not hasattr(norm, "fold"):
+                raise ValueError("a layer that norms its sublayers' outputs takes RMS norms")
+
+    def parts(self):
+        s = self.spec
+        out = [(self.mixer_norm, s.mixer_norm.prefix), (self.mixer, s.mixer.prefix)]
+        if self.mixer_gate is not None:
+            out.append((self.mixer_gate, s.mixer_gate.prefix))
+        if self.feed_forward is not None:
+            out += [(self.feed_forward_norm, s.feed_forward_norm.prefix), (self.feed_forward, s.feed_forward.prefix)]
+            if self.feed_forward_gate is not None:
+                out.append((self.feed_forward_gate, s.feed_forward_gate.prefix))
+        return out
+
+    @property
+    def graph_safe(self):
+        return all(part.graph_safe for part, _ in self.parts())
+
+    def _input(self, ctx, x):
+        if ctx.dtype == torch.float32:
+            return x
+        h = ctx.ws.get("sublayer_in", tuple(x.shape), ctx.dtype)
+        ctx.ops.cast(x, h)
+        return h
+
+    def _join(self, ctx, x, h, y, gate, norm):
+        weight, eps = norm.fold()
+        logits = gate.logits(ctx, h) if gate is not None else None
+        bias = gate.bias if gate is not None else None
+        if isinstance(y, BranchOutputs):
+            ctx.ops.sublayer_merge(y.ys, y.weights, eps, x=x, gate=logits, gate_bias=bias, weight=weight, branch_eps=y.eps)
+        else:
+            ctx.ops.sublayer_merge([y], None, eps, x=x, gate=logits, gate_bias=bias, weight=weight)
+
+    def forward(self, ctx, x, cache, pending=None, next_norm=None):
+        ctx.pending_norm = None
+        h = self._input(ctx, x)
+        self._join(ctx, x, h, self.mixer.forward(ctx, h, cache), self.mixer_gate, self.mixer_norm)
+        if self.feed_forward is not None:
+            h = self._input(ctx, x)
+            self._join(ctx, x, h, self.feed_forward.forward(ctx, h), self.feed_forward_gate, self.feed_forward_norm)
         return None

@@ -94,3 +94,42 @@ class GatedFeedForward(FeedForward):
         y = ctx.ws.get("ffn_out", (T, self.width), torch.float32)
         self.ops.linear(act, self.w_down, y)
         return y
+
+
+@register_feed_forward("plain")
+class PlainFeedForward(FeedForward):
+    """``down(act(up h))`` without a gate: ``activation`` is ``"relu2"`` (the square of relu),
+    ``"silu"``, ``"tanh"`` or ``"sigmoid"``, computed in 32-bit on the product's 32-bit result and
+    rounded once. ``names``: the tensors' local names."""
+    graph_safe = True
+
+    def __init__(self, width: int, inner: int, activation: str = "relu2", names=("up", "down"), init_std: float = 0.02):
+        if activation not in ("relu2", "silu", "tanh", "sigmoid"):
+            raise ValueError(f"unknown activation {activation!r}")
+        self.width, self.inner, self.activation = int(width), int(inner), activation
+        self.names = tuple(names)
+        self.init_std = float(init_std)
+
+    def tensors(self):
+        init = ("normal", self.init_std)
+        u, d = self.names
+        return {u: TensorSpec((self.inner, self.width), init=init), d: TensorSpec((self.width, self.inner), init=init)}
+
+    def load(self, tensors, ops, dtype):
+        super().load(tensors, ops, dtype)
+        u, d = self.names
+        self.w_up = tensors[u].contiguous()
+        self.w_down = tensors[d].contiguous()
+
+    def forward(self, ctx, h, residual=None):
+        T = h.shape[0]
+        z = ctx.ws.get("ffn_up", (T, self.inner), torch.float32)
+        self.ops.linear(h, self.w_up, z)
+        act = ctx.ws.get("ffn_act", (T, self.inner), self.dtype)
+        self.ops.activation(z, act, self.activation)
+        if residual is not None:
+            self.ops.linear(act, self.w_down, residual, accumulate=True)
+            return None
+        y = ctx.ws.get("ffn_out", (T, self.width), torch.float32)
+        self.ops.linear(act, self.w_down, y)
+        return y

@@ -274,8 +274,9 @@ class CpuOps:
 
     # ---- the gated delta rule with a decay per key channel ----
     def delta_rule(self, ctx, proj, second, conv_w, a_log, dt_bias, norm_w, eps, state, heads, kv_heads, dim, vdim,
-                   taps, out):
-        """Per request, token by token: the convolution over the kept last inputs and the new one,
+                   taps, out, decay_per_head=False, gate="sigmoid"):
+        """decay_per_head: second = [decay logit per head | gate logits], dt_bias per head; gate: the
+        activation of the gate's logit. Per request, token by token: the convolution over the kept last inputs and the new one,
         SiLU, unit vectors, S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q; then
         o / rms(o) * norm_w * sigmoid(gate)."""
         b = ctx.batch
@@ -303,18 +304,112 @@ class CpuOps:
                 q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dim ** -0.5
                 k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
                 beta = torch.sigmoid(proj[t, C:C + H])
-                g = torch.exp(-rate[:, None] * torch.nn.functional.softplus(second[t, :H * dim] + dt_bias.float()).reshape(H, dim))
-                gate = torch.sigmoid(second[t, H * dim:]).reshape(H, vdim)
+                if decay_per_head:
+                    g = torch.exp(-rate * torch.nn.functional.softplus(second[t, :H] + dt_bias.float()))[:, None].expand(H, dim)
+                    z = second[t, H:]
+                else:
+                    g = torch.exp(-rate[:, None] * torch.nn.functional.softplus(second[t, :H * dim] + dt_bias.float()).reshape(H, dim))
+                    z = second[t, H * dim:]
+                gate_v = (z * torch.sigmoid(z) if gate == "silu" else torch.sigmoid(z)).reshape(H, vdim)
                 for n in range(H):
                     kk, qq = k[n // (H // G)], q[n // (H // G)]
                     S[n] = g[n][:, None] * S[n]
                     u = beta[n] * (v[n] - S[n].t() @ kk)
                     S[n] = S[n] + kk[:, None] * u[None, :]
                     o = S[n].t() @ qq
-                    o = o / torch.sqrt((o * o).mean() + eps) * norm_w.float() * gate[n]
+                    o = o / torch.sqrt((o * o).mean() + eps) * norm_w.float() * gate_v[n]
                     out[t, n * vdim:(n + 1) * vdim] = o.to(out.dtype)
             state[slot, :n_state] = S.reshape(-1)
             state[slot, n_state:] = kept.reshape(-1)
+
+    # ---- the generalized delta rule ----
+    def general_delta(self, ctx, proj, cols, zdec, w0, a0, decay_scale, norm_w, eps, state, heads, dim, vdim, out):
+        """Per request, token by token: w = exp(-c sigmoid(zdec + w0)), a = sigmoid(logit + a0), u the
+        unit key; S <- diag(w) S - (a u)(u^T S) + k v^T from the old S; o = S^T r; then per head
+        o / rms(o) * norm_w * sigmoid(gate)."""
+        b = ctx.batch
+        H = heads
+        cr, ck, cv, ca, cg = cols
+        cu, slots = b.cu_q.tolist(), b.slots.tolist()
+        for r_i, slot in enumerate(slots):
+            if slot < 0:
+                out[cu[r_i]:cu[r_i + 1]] = 0
+                continue
+            S = state[slot].reshape(H, dim, vdim).clone()
+            for t in range(cu[r_i], cu[r_i + 1]):
+                row = proj[t]
+                r = row[cr:cr + H * dim].reshape(H, dim)
+                k = row[ck:ck + H * dim].reshape(H, dim)
+                v = row[cv:cv + H * vdim].reshape(H, vdim)
+                a = torch.sigmoid(row[ca:ca + H * dim] + a0).reshape(H, dim)
+                w = torch.exp(-decay_scale * torch.sigmoid(zdec[t, :H * dim] + w0)).reshape(H, dim)
+                gate = torch.sigmoid(row[cg:cg + H * vdim]).reshape(H, vdim)
+                u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+                for n in range(H):
+                    S[n] = w[n][:, None] * S[n] - (a[n] * u[n])[:, None] * (u[n] @ S[n])[None, :] + k[n][:, None] * v[n][None, :]
+                    o = S[n].t() @ r[n]
+                    o = o / torch.sqrt((o * o).mean() + eps) * norm_w[n * vdim:(n + 1) * vdim] * gate[n]
+                    out[t, n * vdim:(n + 1) * vdim] = o.to(out.dtype)
+            state[slot] = S.reshape(-1)
+
+    # ---- normed queries and keys; sublayers whose outputs are normed ----
+    def qk_norm_rope_append(self, src, cols, q_out, k_pool, v_pool, positions, token_req, block_table, heads, kv_heads,
+                            dim, vdim, q_weight, k_weight, eps, rotary, page_size):
+        """queries and keys normed per head (weights 32-bit; None: not), rotated, queries out, keys and
+        the untouched value columns into their pages"""
+        T = src.shape[0]
+        cq, ck, cv = cols
+        q = src[:, cq:cq + heads * dim].float().reshape(T, heads, dim)
+        k = src[:, ck:ck + kv_heads * dim].float().reshape(T, kv_heads, dim)
+        v = src[:, cv:cv + kv_heads * vdim].float().reshape(T, kv_heads, vdim)
+        if q_weight is not None:
+            q = q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps) * q_weight.reshape(heads, dim)
+        if k_weight is not None:
+            k = k / torch.sqrt((k * k).mean(-1, keepdim=True) + eps) * k_weight
+        if rotary is not None:
+            q, k = self._rotate(q, positions, rotary), self._rotate(k, positions, rotary)
+        q_out.copy_(q.to(q_out.dtype))
+        for t in range(T):
+            pos = int(positions[t])
+            page = int(block_table[int(token_req[t]), pos // page_size])
+            if page >= 0:
+                k_pool[page, :, pos % page_size, :] = k[t].to(k_pool.dtype)
+                v_pool[page, :, pos % page_size, :] = v[t].to(v_pool.dtype)
+
+    @staticmethod
+    def _unary(z, kind):
+        if kind == "sigmoid":
+            return torch.sigmoid(z)
+        if kind == "silu":
+            return z * torch.sigmoid(z)
+        if kind == "relu2":
+            return torch.relu(z) ** 2
+        if kind == "tanh":
+            return torch.tanh(z)
+        raise ValueError(kind)
+
+    def gate_mul(self, x, gate, kind="sigmoid"):
+        x.copy_((x.float() * self._unary(gate.float(), kind)).to(x.dtype))
+
+    def activation(self, z, out, kind):
+        out.copy_(self._unary(z.float(), kind).to(out.dtype))
+
+    def sublayer_merge(self, ys, branch_weights, eps, x=None, out=None, gate=None, gate_bias=None, weight=None,
+                       branch_eps=None):
+        """y = mean_b rms(y_b) w_b (or the one y); y *= sigmoid(gate + bias); x += rms(y) weight (or out = y)"""
+        def rms(v, e):
+            return v / torch.sqrt((v * v).mean(-1, keepdim=True) + e)
+        if branch_weights is not None:
+            be = eps if branch_eps is None else branch_eps
+            y = sum(rms(yb, be) * wb for yb, wb in zip(ys, branch_weights)) / len(ys)
+        else:
+            y = ys[0]
+        if gate is not None:
+            y = y * torch.sigmoid(gate + (gate_bias if gate_bias is not None else 0.0))
+        if x is None:
+            out.copy_(y)
+        else:
+            x += rms(y, eps) * weight
 
     def latent_append(self, src, norm_w, eps, rank, rot, rotary, positions, token_req, block_table, pool, page_size):
         """rows [rms(src[:, :rank]) * w | rotate(src[:, rank:])] into their pages"""
