@@ -17,7 +17,7 @@ def rms(x, eps):
 
 
 def sigmoid(z):
-    return 1.0 / (1.0 + np.exp(-z))
+    return 0.5 * (1.0 + np.tanh(0.5 * z))
 
 
 def silu(z):
