@@ -6,6 +6,7 @@
     python bench.py --shape tinyllama|llama2-7b|llama3-8b [--layers L]
 
     python bench.py --design murilorn [--size 2k,4k]    (likewise for the third architecture)
+    python bench.py --design luvapel [--size 2k,4k]     (the fourth, beside the third)
     python bench.py --design kavenex [--size 2k,4k]     (a JSON line of its own: the second architecture
                                                          beside Llama at equal sizes, kernel beside like kernel)
 
@@ -855,6 +856,256 @@ def run_design_murilorn(args) -> dict:
     return out
 
 
+# ``--design luvapel``: the Luvapel design beside the Murilorn decoder (the closest of the engine's models: a
+# delta rule and windowed attention) at equal width, heads, head sizes and depth (random weights). Four layers:
+# generalized delta rule, mixers side by side (windowed attention and a gated delta rule), and again; every
+# layer with a dense feed-forward as large as a Murilorn token's experts together.
+LUVAPEL_SIZES = {
+    "2k": dict(width=2048, heads=32, kv_heads=4, dim=64, window=1024, rot_dims=32, g_heads=32, g_dim=64, rank=64,
+               d_heads=16, d_kv_heads=16, d_dim=128, d_vdim=128, taps=4, ff=5632, experts=16, top=4, expert_ff=1408, vocab=32000),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, window=1024, rot_dims=64, g_heads=32, g_dim=128, rank=128,
+               d_heads=32, d_kv_heads=16, d_dim=128, d_vdim=128, taps=4, ff=11008, experts=16, top=4, expert_ff=2752, vocab=32000),
+}
+
+
+def luvapel_configs(z):
+    ff = {"kind": "dense", "ff": z["ff"]}
+    general = {"type": "general_delta", "mixer": {"heads": z["g_heads"], "dim": z["g_dim"], "decay_rank": z["rank"]}, "mlp": ff}
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+            "mask": {"size": z["window"]}, "rot": {"base": 10000.0, "dims": z["rot_dims"]}}
+    right = {"heads": z["d_heads"], "kv_heads": z["d_kv_heads"], "dim": z["d_dim"], "vdim": z["d_vdim"], "conv": z["taps"]}
+    parallel = {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": ff}
+    luvapel = {"architecture": "Luvapel", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0},
+               "norm": {"eps": 1e-5}, "max_positions": 4096, "layers": [general, parallel, general, parallel]}
+    attn = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                                           "scale": z["dim"] ** -0.5, "softcap": 30.0, "mask": {"size": z["window"], "keep_first": 4}}}
+    delta = {"type": "channel_delta", "mixer": {"heads": z["d_heads"], "kv_heads": z["d_kv_heads"], "dim": z["d_dim"],
+                                                "vdim": z["d_vdim"], "conv": z["taps"], "decay_rank": z["rank"], "gate_rank": z["rank"]}}
+    moe = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["expert_ff"]}}
+    murilorn = {"architecture": "Murilorn", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0},
+                "norm": {"eps": 1e-5}, "streams": 2, "logit_scale": 1.0, "logit_softcap": 30.0, "max_positions": 4096,
+                "layers": [dict(m, mlp=moe) for m in (delta, attn, delta, attn)]}
+    return luvapel, murilorn
+
+
+def run_design_luvapel(args) -> dict:
+    """Prefill and decode throughput of the Luvapel design and of the Murilorn decoder at equal sizes, and
+    the design's kernels beside the like kernels of Murilorn (or of Llama, where those are the like ones),
+    each against its roofline (the slower of bytes / measured copy rate and FLOPs / measured bfloat16 rate)."""
+    import numpy as np
+    import torch
+    from garuda_b200 import Engine, StepEntry
+    from garuda_b200.engine.batch import Workspace
+    from garuda_b200.parts.attention import NormedKeyAttention
+    from garuda_b200.weights import write_random_model
+
+    hbm_peak, tflops_peak, peak_kind = peaks()
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    dev = torch.device("cuda:0")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(reps):
+            flush.zero_()
+            s, e = ev(), ev()
+            torch.cuda.synchronize()
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e))
+        return sorted(times)[len(times) // 2]
+
+    def roof(ms, flops=0.0, nbytes=0.0):
+        ideal = max(flops / (tflops_peak * 1e12), nbytes / (hbm_peak * 1e9)) * 1e3
+        return {"ms": round(ms, 4), "roofline_ms": round(ideal, 4), "frac": round(ideal / ms, 4)}
+
+    out = {"design": "luvapel", "beside": "murilorn", "peaks": peak_kind, "hbm_gbs": hbm_peak, "bf16_tflops": tflops_peak,
+           "dtype": "bf16", "data": "synthetic",
+           "timing": "CUDA events, 3 warm-up runs, L2 flushed before every timed run, median", "sizes": {}}
+    B, CTX, T = 8, 2048, PREFILL_TOKENS
+    for name in (args.size.split(",") if args.size else list(LUVAPEL_SIZES)):
+        z = LUVAPEL_SIZES[name]
+        rec, engines = {}, {}
+        for arch, cfg in zip(("luvapel", "murilorn"), luvapel_configs(z)):
+            tmp = tempfile.mkdtemp(prefix="garuda_bench_", dir="/dev/shm" if os.path.isdir("/dev/shm") else None)
+            try:
+                write_random_model(tmp, cfg, seed=0, store_dtype=torch.bfloat16)
+                engine = Engine(tmp, dtype="bfloat16", context=4096, page_size=32, kv_tokens=B * CTX + 4096 + 64,
+                                max_concurrent=B, max_batch_tokens=T, prefill_chunk=T, ignore_eos=True)
+            finally:
+                shutil.rmtree(tmp, ignore_errors=True)
+            engines[arch] = engine
+            runner, rng, V = engine.runner, np.random.default_rng(0), z["vocab"]
+            toks = rng.integers(0, V, T).tolist()
+            rid = [0]
+
+            def prefill():
+                rid[0] += 1
+                runner.run([StepEntry(10_000 + rid[0], toks, [T - 1])])
+                runner.end(10_000 + rid[0])
+
+            ms = timed(prefill, reps=5)
+            rec[arch] = {"prefill_2048_ms": round(ms, 3), "prefill_tok_s": round(T / ms * 1e3)}
+            steps = 48
+            for r in range(B):
+                runner.run([StepEntry(r, rng.integers(0, V, CTX - steps - 8).tolist(), [])])
+            feed = rng.integers(0, V, (steps + 8, B))
+            for i in range(8):
+                runner.run([StepEntry(r, [int(feed[i, r])], [0]) for r in range(B)])
+            marks = [ev() for _ in range(steps + 1)]
+            torch.cuda.synchronize()
+            marks[0].record()
+            for i in range(steps):
+                runner.run([StepEntry(r, [int(feed[8 + i, r])], [0]) for r in range(B)])
+                marks[i + 1].record()
+            torch.cuda.synchronize()
+            each = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
+            for r in range(B):
+                runner.end(r)
+            rec[arch].update({"decode_b8_ctx2048_ms": round(each[len(each) // 2], 4),
+                              "decode_tok_s": round(B / each[len(each) // 2] * 1e3),
+                              "graph_replays": runner.graphs.replays,
+                              "kernels_per_decode_step": runner.graphs.launches_replayed(B)})
+            if engine.ops.tc is not None:
+                engine.ops.tc.check_errors()
+        # ------------------------------------------------------------ kernel beside like kernel
+        ops = engines["luvapel"].ops
+        bf = torch.bfloat16
+        H, Hkv, hd, W, ps, win = z["heads"], z["kv_heads"], z["dim"], z["width"], 32, z["window"]
+        ws = Workspace(dev)
+
+        class Ctx:
+            pass
+        ctx = Ctx()
+        ctx.ws = ws
+        ctx.step_cache = {}
+        kern = {}
+        for label, nreq, q_len, kv_len in (("prefill_2048", 1, T, T), ("decode_b8_ctx2048", B, 1, CTX)):
+            pages = (kv_len + ps - 1) // ps
+            bt = torch.arange(nreq * pages, dtype=torch.int32, device=dev).view(nreq, pages)
+            cu = torch.arange(nreq + 1, dtype=torch.int32, device=dev) * q_len
+            kvl = torch.full((nreq,), kv_len, dtype=torch.int32, device=dev)
+            req = torch.arange(nreq, dtype=torch.int32, device=dev).repeat_interleave(q_len)
+            q = torch.randn(nreq * q_len, H, hd, device=dev).to(bf)
+            kp, vp = (torch.randn(nreq * pages, Hkv, ps, hd, device=dev).to(bf) for _ in range(2))
+            o = torch.empty(nreq * q_len, H * hd, dtype=bf, device=dev)
+            keys = nreq * sum(min(p + 1, win) for p in range(kv_len - q_len, kv_len))
+            read = nreq * min(kv_len, win + q_len)
+            cost = (4.0 * H * hd * keys, 2.0 * (2 * read * Hkv * hd + q.numel() + o.numel()))
+            ms = timed(lambda: ops.paged_attention(q, kp, vp, bt, cu, kvl, req, o, hd ** -0.5, win, ps, nreq, q_len, kv_len, ws=ws,
+                                                   min_q_len=q_len))
+            kern[f"windowed_attention_{label}"] = roof(ms, *cost)
+            ms = timed(lambda: ops.paged_attention(q, kp, vp, bt, cu, kvl, req, o, hd ** -0.5, win, ps, nreq, q_len, kv_len, ws=ws,
+                                                   min_q_len=q_len, softcap=30.0, keep_first=4, sink=True))
+            kern[f"murilorn_capped_sink_attention_{label}"] = roof(ms, *cost)
+            # the projected row into queries and pages: normed and rotated here, biased there
+            n = nreq * q_len
+            pos = (torch.arange(q_len, dtype=torch.int32, device=dev) + (kv_len - q_len)).repeat(nreq)
+            row = torch.randn(n, (H + 3 * Hkv) * hd, device=dev)
+            part = NormedKeyAttention(W, H, Hkv, hd, rot_base=10000.0, rot_dims=z["rot_dims"])
+            qw, kw = torch.ones(H, hd, device=dev), torch.ones(hd, device=dev)
+            moved = 4.0 * n * (H + Hkv) * hd + 2.0 * n * (H + 2 * Hkv) * hd
+            ms = timed(lambda: ops.qk_norm_rope_append(row, (0, H * hd, H * hd), q, kp, vp, pos, req, bt, H, Hkv, hd, hd, qw, kw,
+                                                       1e-5, part.rotary, ps))
+            kern[f"norm_rotate_store_{label}"] = roof(ms, 0, moved)
+            bias = torch.zeros((H + 2 * Hkv) * hd, device=dev)
+            rowm = torch.randn(n, (H + 2 * Hkv) * hd, device=dev)
+            ms = timed(lambda: ops.qkv_bias_append(rowm, bias, q, kp, vp, pos, req, bt, H, Hkv, hd, hd, ps))
+            kern[f"murilorn_bias_store_{label}"] = roof(ms, 0, 4.0 * rowm.numel() + 2.0 * rowm.numel())
+        # feed-forwards: relu^2 of one product here, SiLU-gate of two in Llama's (the dense like kernel)
+        FF = z["ff"]
+        for label, M in (("2048_tokens", T), ("8_tokens", B)):
+            h = torch.randn(M, W, device=dev).to(bf)
+            x = torch.zeros(M, W, device=dev)
+            up, dwn = (torch.randn(FF, W, device=dev) * 0.02).to(bf), (torch.randn(W, FF, device=dev) * 0.02).to(bf)
+            zbuf, act = torch.empty(M, FF, device=dev), torch.empty(M, FF, dtype=bf, device=dev)
+
+            def plain():
+                ops.linear(h, up, zbuf)
+                ops.activation(zbuf, act, "relu2")
+                ops.linear(act, dwn, x, accumulate=True)
+
+            kern[f"relu2_feed_forward_{label}"] = roof(timed(plain), 2.0 * M * 2 * FF * W, 2.0 * 2 * FF * W)
+            g = ops.pack_gate_up((torch.randn(FF, W, device=dev) * 0.02).to(bf), (torch.randn(FF, W, device=dev) * 0.02).to(bf))
+
+            def dense():
+                ops.linear_gated(ctx, h, g, act, "silu", 0.0)
+                ops.linear(act, dwn, x, accumulate=True)
+
+            kern[f"llama_silu_feed_forward_{label}"] = roof(timed(dense), 2.0 * M * 3 * FF * W, 2.0 * 3 * FF * W)
+            del up, dwn, g, zbuf, act
+        # the recurrent mixers: bytes are their rows in and out and the state
+
+        class Bt:
+            pass
+        dH, dG, dd, dv, taps = z["d_heads"], z["d_kv_heads"], z["d_dim"], z["d_vdim"], z["taps"]
+        gH, gd = z["g_heads"], z["g_dim"]
+        C = 2 * dG * dd + dH * dv
+        conv_w, a_log = torch.randn(C, taps, device=dev) * 0.3, torch.randn(dH, device=dev) * 0.3
+        nw = torch.ones(dv, device=dev)
+        state = torch.zeros(B, dH * dd * dv + (taps - 1) * C, device=dev)
+        gstate = torch.zeros(B, gH * gd * gd, device=dev)
+        HD = gH * gd
+        w0, a0, gnw = torch.randn(HD, device=dev), torch.randn(HD, device=dev), torch.ones(HD, device=dev)
+        for label, nreq, q_len in (("prefill_2048", 1, T), ("decode_b8", B, 1)):
+            b = Bt()
+            b.cu_q = torch.arange(nreq + 1, dtype=torch.int32, device=dev) * q_len
+            b.slots = torch.arange(nreq, dtype=torch.int32, device=dev)
+            b.token_req = torch.arange(nreq, dtype=torch.int32, device=dev).repeat_interleave(q_len)
+            b.num_requests, b.max_q_len = nreq, q_len
+            ctx.batch = b
+            n = nreq * q_len
+            proj = torch.randn(n, C + dH, device=dev)
+            o = torch.empty(n, dH * dv, dtype=bf, device=dev)
+            second = torch.randn(n, dH + dH * dv, device=dev)
+            dtb = torch.randn(dH, device=dev)
+            ms = timed(lambda: ops.delta_rule(ctx, proj, second, conv_w, a_log, dtb, nw, 1e-5, state, dH, dG, dd, dv, taps, o,
+                                              decay_per_head=True, gate="silu"))
+            kern[f"head_delta_rule_{label}"] = roof(ms, 0, 4.0 * (proj.numel() + second.numel()) + 2.0 * o.numel()
+                                                    + 2 * 4.0 * nreq * state.shape[1])
+            second = torch.randn(n, dH * dd + dH * dv, device=dev)
+            dtb = torch.randn(dH * dd, device=dev)
+            ms = timed(lambda: ops.delta_rule(ctx, proj, second, conv_w, a_log, dtb, nw, 1e-5, state, dH, dG, dd, dv, taps, o))
+            kern[f"murilorn_channel_delta_rule_{label}"] = roof(ms, 0, 4.0 * (proj.numel() + second.numel()) + 2.0 * o.numel()
+                                                                + 2 * 4.0 * nreq * state.shape[1])
+            gproj, zdec = torch.randn(n, 5 * HD, device=dev), torch.randn(n, HD, device=dev)
+            go = torch.empty(n, HD, dtype=bf, device=dev)
+            ms = timed(lambda: ops.general_delta(ctx, gproj, (0, HD, 2 * HD, 3 * HD, 4 * HD), zdec, w0, a0, 0.6, gnw, 1e-5, gstate,
+                                                 gH, gd, gd, go))
+            kern[f"general_delta_rule_{label}"] = roof(ms, 0, 4.0 * (gproj.numel() + zdec.numel()) + 2.0 * go.numel()
+                                                       + 2 * 4.0 * nreq * gstate.shape[1])
+        # what joins a sublayer to the residual: two branches, gate, norm and sum here; two streams there
+        ys = [torch.randn(T, W, device=dev) for _ in range(2)]
+        bw = [torch.ones(W, device=dev) for _ in range(2)]
+        gate, gb_, wv = torch.randn(T, W, device=dev), torch.zeros(W, device=dev), torch.ones(W, device=dev)
+        xr, hb = torch.randn(T, W, device=dev), torch.empty(T, W, dtype=bf, device=dev)
+        kern["branches_gate_norm_add_2048_tokens"] = roof(
+            timed(lambda: ops.sublayer_merge(ys, bw, 1e-5, x=xr, gate=gate, gate_bias=gb_, weight=wv, rounded=hb)), 0,
+            (4.0 * 5 + 2.0) * T * W)
+        kern["gate_norm_add_2048_tokens"] = roof(
+            timed(lambda: ops.sublayer_merge(ys[:1], None, 1e-5, x=xr, gate=gate, gate_bias=gb_, weight=wv, rounded=hb)), 0,
+            (4.0 * 4 + 2.0) * T * W)
+        S = 2
+        xs, y = torch.randn(T, S, W, device=dev), torch.randn(T, W, device=dev)
+        a_in, b_out, mix = torch.ones(S, device=dev), torch.ones(S, device=dev), torch.eye(S, device=dev).contiguous()
+        on = torch.empty(T, W, dtype=bf, device=dev)
+        kern["murilorn_streams_write_and_read_2048_tokens"] = roof(
+            timed(lambda: ops.streams_update(xs, mix, b_out, y, next_in=a_in, norm_weight=wv, eps=1e-5, normed=on)), 0,
+            (8.0 * S + 4.0 + 2.0) * T * W)
+        octx = torch.randn(T, H * hd, device=dev).to(bf)
+        kern["output_gate_2048_tokens"] = roof(timed(lambda: ops.gate_mul(octx, gate[:, :H * hd], "sigmoid")), 0, (4.0 + 4.0) * T * H * hd)
+        rec["kernels"] = kern
+        rec["config"] = {k: v for k, v in z.items()}
+        out["sizes"][name] = rec
+        del engines
+        torch.cuda.empty_cache()
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -869,8 +1120,9 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=0, help="context reached with --only decode (default: the shape's); keys with --only attention")
     ap.add_argument("--layers", type=int, default=0,
                     help="fewer layers than the configuration has (reported beside the full number)")
-    ap.add_argument("--design", choices=["kavenex", "murilorn"],
-                    help="instead of the default workload: this design beside the Llama decoder at equal sizes")
+    ap.add_argument("--design", choices=["kavenex", "murilorn", "luvapel"],
+                    help="instead of the default workload: this design beside the Llama decoder (luvapel: beside "
+                         "Murilorn, the closest of the engine's models) at equal sizes")
     ap.add_argument("--size", default="", help="with --design: which of its sizes (2k, 4k; default both)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -887,7 +1139,8 @@ def main() -> int:
         print("bench.py: --batch must be 1 to 64")
         return 2
     if args.design:
-        print(json.dumps(run_design_murilorn(args) if args.design == "murilorn" else run_design(args)))
+        run = {"murilorn": run_design_murilorn, "luvapel": run_design_luvapel, "kavenex": run_design}[args.design]
+        print(json.dumps(run(args)))
         return 0
     print(json.dumps(run_ours(args)))
     return 0

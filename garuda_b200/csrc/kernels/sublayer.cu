@@ -10,6 +10,7 @@
 //   sublayer_merge       y = alpha * sum_b rms(y_b) * w_b   (or y = y_0)
 //                        y <- y * sigmoid(gate + bias)      (optional)
 //                        x <- x + rms(y) * w                (or out = y)
+//                        h = x rounded to bfloat16          (optional: the next sublayer's input)
 #include "common.cuh"
 
 namespace {
@@ -137,7 +138,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 __global__ void __launch_bounds__(256)
 sublayer_merge_kernel(Branches br, float alpha, float branch_eps, const float* __restrict__ gate, int gate_stride,
                       const float* __restrict__ gate_bias, const float* __restrict__ w, float eps, float* __restrict__ x,
-                      float* __restrict__ out, int d) {
+                      float* __restrict__ out, __nv_bfloat16* __restrict__ rounded, int d) {
   extern __shared__ float rowbuf[];       // [d]
   __shared__ float red[8];
   gb::pdl_launch_dependents();
@@ -169,7 +170,11 @@ sublayer_merge_kernel(Branches br, float alpha, float branch_eps, const float* _
   float ss = 0.f;
   for (int c = threadIdx.x; c < d; c += blockDim.x) ss = fmaf(rowbuf[c], rowbuf[c], ss);
   const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
-  for (int c = threadIdx.x; c < d; c += blockDim.x) x[t * d + c] += (rowbuf[c] * inv) * w[c];
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float v = x[t * d + c] + (rowbuf[c] * inv) * w[c];
+    x[t * d + c] = v;
+    if (rounded != nullptr) rounded[t * d + c] = __float2bfloat16_rn(v);
+  }
 }
 
 int grid_for(long long total, int block) {
@@ -226,14 +231,16 @@ GB_EXPORT int gb_unary_act(const void* z, int z_dtype, int z_stride, void* out, 
 }
 
 // ys, ws: `branches` pointers each (ws null: y = ys[0] as it is). x null: the merged row goes to `out`.
+// rounded (bfloat16 [T, d], optional): the new x rounded, for the sublayer that reads it next.
 GB_EXPORT int gb_sublayer_merge(const float* const* ys, const float* const* ws, int branches, float alpha, float branch_eps,
                                 const float* gate, int gate_stride, const float* gate_bias, const float* w, float eps,
-                                float* x, float* out, int T, int d, cudaStream_t stream) {
+                                float* x, float* out, void* rounded, int T, int d, cudaStream_t stream) {
   if (T <= 0) return GB_OK;
   if (branches < 1 || branches > MAX_BRANCHES) return gb::fail(GB_UNSUPPORTED, "sublayer_merge: %d branches (1 to %d)", branches, MAX_BRANCHES);
   if (ws == nullptr && branches != 1) return gb::fail(GB_BAD_ARGUMENT, "sublayer_merge: several branches need their weights");
   if ((x == nullptr) == (out == nullptr)) return gb::fail(GB_BAD_ARGUMENT, "sublayer_merge: either x or out");
   if (x != nullptr && w == nullptr) return gb::fail(GB_BAD_ARGUMENT, "sublayer_merge: the norm's weight is missing");
+  if (rounded != nullptr && x == nullptr) return gb::fail(GB_BAD_ARGUMENT, "sublayer_merge: a rounded copy is of x");
   const size_t smem = (size_t)d * sizeof(float);
   if (smem > 48 * 1024) return gb::fail(GB_UNSUPPORTED, "sublayer_merge: rows of %d (at most 12288)", d);
   Branches br = {};
@@ -243,6 +250,6 @@ GB_EXPORT int gb_sublayer_merge(const float* const* ys, const float* const* ws, 
     br.w[b] = ws ? ws[b] : nullptr;
   }
   return gb::check_pdl_launch(gb::launch_pdl(sublayer_merge_kernel, dim3(T), dim3(256), smem, stream, dim3(1, 1, 1), br, alpha,
-                                             branch_eps, gate, gate_stride, gate_bias, w, eps, x, out, d),
+                                             branch_eps, gate, gate_stride, gate_bias, w, eps, x, out, (__nv_bfloat16*)rounded, d),
                               "sublayer_merge");
 }

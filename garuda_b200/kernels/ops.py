@@ -213,7 +213,7 @@ class CudaOps:
         "gb_gate_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "gb_unary_act": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "gb_sublayer_merge": [c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_int, c_void_p, c_void_p, c_float,
-                              c_void_p, c_void_p, c_int, c_int, c_void_p],
+                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     }
 
     _MIXER_SIGNATURES = {
@@ -1066,14 +1066,16 @@ class CudaOps:
                                       self._stream()), "activation")
 
     def sublayer_merge(self, ys, branch_weights, eps, x=None, out=None, gate=None, gate_bias=None, weight=None,
-                       branch_eps=None):
+                       branch_eps=None, rounded=None):
         """What stands between a sublayer's output and the residual where the output, not the input, is
         normed. ``ys``: one 32-bit ``[T, d]`` output, or several branches' with ``branch_weights`` (32-bit
         ``[d]`` each): ``y = mean_b rms(y_b) * w_b``. ``gate`` (32-bit logits ``[T, d]``, a column range
         will do) and ``gate_bias [d]``: ``y <- y * sigmoid(gate + gate_bias)``. Then ``x += rms(y) *
-        weight`` (``x`` the 32-bit residual), or with ``out`` in place of ``x``: ``out = y``. One pass."""
+        weight`` (``x`` the 32-bit residual), or with ``out`` in place of ``x``: ``out = y``. ``rounded``
+        (bfloat16 ``[T, d]``): also the new ``x`` rounded, the input of the sublayer that reads it next.
+        One pass."""
         ys = list(ys)
-        self._on_device(*ys, x, out, gate, gate_bias, weight)
+        self._on_device(*ys, x, out, gate, gate_bias, weight, rounded)
         T, d = ys[0].shape
         _need(all(y.dtype == torch.float32 and y.is_contiguous() and tuple(y.shape) == (T, d) for y in ys),
               "sublayer_merge: float32 [T, d] outputs")
@@ -1090,6 +1092,8 @@ class CudaOps:
               "sublayer_merge: x or out float32 [T, d]")
         _need(x is None or (weight is not None and weight.dtype == torch.float32 and weight.numel() == d),
               "sublayer_merge: the norm's float32 weight")
+        _need(rounded is None or (x is not None and rounded.dtype == torch.bfloat16 and rounded.is_contiguous()
+                                  and tuple(rounded.shape) == (T, d)), "sublayer_merge: rounded bfloat16 [T, d] beside x")
         n = len(ys)
         y_ptrs = (c_void_p * n)(*[y.data_ptr() for y in ys])
         w_ptrs = (c_void_p * n)(*[w.data_ptr() for w in ws]) if ws is not None else None
@@ -1097,7 +1101,7 @@ class CudaOps:
         self._check(L, L.gb_sublayer_merge(
             y_ptrs, w_ptrs, n, 1.0 / n, float(eps if branch_eps is None else branch_eps), _ptr(gate),
             gate.stride(0) if gate is not None else 0, _ptr(gate_bias), _ptr(weight), float(eps), _ptr(x),
-            None if x is not None else out.data_ptr(), T, d, self._stream()), "sublayer_merge")
+            None if x is not None else out.data_ptr(), _ptr(rounded), T, d, self._stream()), "sublayer_merge")
 
     # ------------------------------------------------------------------ sampling
     def argmax(self, logits, out):

@@ -222,27 +222,58 @@ class SublayerNormBlock:
     def graph_safe(self):
         return all(part.graph_safe for part, _ in self.parts())
 
-    def _input(self, ctx, x):
+    def takes_pending_norm(self, ops):
+        """What the layer in front may leave for this one: nothing to fold, but a layer of the same
+        arrangement writes this layer's rounded input in its last pass over the row."""
+        return _ROUNDED_INPUT
+
+    def _input(self, ctx, x, turn=0):
         if ctx.dtype == torch.float32:
             return x
-        h = ctx.ws.get("sublayer_in", tuple(x.shape), ctx.dtype)
+        h = ctx.ws.get(f"sublayer_in_{turn}", tuple(x.shape), ctx.dtype)
         ctx.ops.cast(x, h)
         return h
 
-    def _join(self, ctx, x, h, y, gate, norm):
+    def _join(self, ctx, x, h, y, gate, norm, turn=None):
+        """``x += norm(gate(h) * y)``. ``turn``: also write the new ``x`` rounded to the compute dtype
+        into that buffer and return it (the next sublayer's input)."""
         weight, eps = norm.fold()
         logits = gate.logits(ctx, h) if gate is not None else None
         bias = gate.bias if gate is not None else None
+        rounded = None
+        if turn is not None and ctx.dtype == torch.bfloat16:
+            rounded = ctx.ws.get(f"sublayer_in_{turn}", tuple(x.shape), ctx.dtype)
         if isinstance(y, BranchOutputs):
-            ctx.ops.sublayer_merge(y.ys, y.weights, eps, x=x, gate=logits, gate_bias=bias, weight=weight, branch_eps=y.eps)
+            ctx.ops.sublayer_merge(y.ys, y.weights, eps, x=x, gate=logits, gate_bias=bias, weight=weight, branch_eps=y.eps,
+                                   rounded=rounded)
         else:
-            ctx.ops.sublayer_merge([y], None, eps, x=x, gate=logits, gate_bias=bias, weight=weight)
+            ctx.ops.sublayer_merge([y], None, eps, x=x, gate=logits, gate_bias=bias, weight=weight, rounded=rounded)
+        return rounded
 
     def forward(self, ctx, x, cache, pending=None, next_norm=None):
+        """``pending``: this layer's input already rounded, by the layer in front. ``next_norm``: what
+        the next layer said it takes; if that is a rounded input, the last pass writes it and it is
+        returned."""
         ctx.pending_norm = None
-        h = self._input(ctx, x)
-        self._join(ctx, x, h, self.mixer.forward(ctx, h, cache), self.mixer_gate, self.mixer_norm)
-        if self.feed_forward is not None:
-            h = self._input(ctx, x)
-            self._join(ctx, x, h, self.feed_forward.forward(ctx, h), self.feed_forward_gate, self.feed_forward_norm)
-        return None
+        last = 1 if next_norm is _ROUNDED_INPUT else None
+        h = pending if pending is not None else self._input(ctx, x, 1)
+        ff = self.feed_forward
+        # two buffers in turn: a sublayer's input is read by its gate while the pass writes the next one
+        h2 = self._join(ctx, x, h, self.mixer.forward(ctx, h, cache), self.mixer_gate, self.mixer_norm,
+                        turn=0 if ff is not None else last)
+        if ff is None:
+            return h2
+        if h2 is None:
+            h2 = self._input(ctx, x, 0)
+        return self._join(ctx, x, h2, ff.forward(ctx, h2), self.feed_forward_gate, self.feed_forward_norm, turn=last)
+
+
+class _RoundedInput:
+    """Marker: the next layer takes its input (the residual rounded to the compute dtype) from
+    the pass that last wrote the residual."""
+
+    def __repr__(self):
+        return "rounded input"
+
+
+_ROUNDED_INPUT = _RoundedInput()

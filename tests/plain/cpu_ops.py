@@ -395,7 +395,7 @@ class CpuOps:
         out.copy_(self._unary(z.float(), kind).to(out.dtype))
 
     def sublayer_merge(self, ys, branch_weights, eps, x=None, out=None, gate=None, gate_bias=None, weight=None,
-                       branch_eps=None):
+                       branch_eps=None, rounded=None):
         """y = mean_b rms(y_b) w_b (or the one y); y *= sigmoid(gate + bias); x += rms(y) weight (or out = y)"""
         def rms(v, e):
             return v / torch.sqrt((v * v).mean(-1, keepdim=True) + e)
@@ -410,6 +410,8 @@ class CpuOps:
             out.copy_(y)
         else:
             x += rms(y, eps) * weight
+            if rounded is not None:
+                rounded.copy_(x.to(rounded.dtype))
 
     def latent_append(self, src, norm_w, eps, rank, rot, rotary, positions, token_req, block_table, pool, page_size):
         """rows [rms(src[:, :rank]) * w | rotate(src[:, rank:])] into their pages"""

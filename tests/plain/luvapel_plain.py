@@ -78,7 +78,7 @@ def causal_conv(x, w):
     """x [T, C], w [C, taps]: y[t, c] = sum_j w[c, taps-1-j] x[t-j, c], zeros before the start."""
     T, taps = x.shape[0], w.shape[1]
     y = np.zeros_like(x)
-    for j in range(taps):
+    for j in range(min(taps, T)):
         y[j:] += x[:T - j] * w[:, taps - 1 - j]
     return y
 
