@@ -108,7 +108,9 @@ struct EpilogueArgs {
   float gate_limit = 0.f;
 };
 
-enum GateAct : int { GATE_SILU = 0, GATE_GELU_TANH = 1, GATE_CLAMPED_SWISH = 2 };
+enum GateAct : int { GATE_SILU = 0, GATE_GELU_TANH = 1, GATE_CLAMPED_SWISH = 2,
+                     // of one value, in the storing epilogue (EPI_STORE | EPI_GENERAL, bfloat16 out): relu(z)^2, tanh(z)
+                     STORE_RELU2 = 3, STORE_TANH = 4 };
 
 // This CTA's slice of `bytes` at `base` into L2 (cta of ctas; 16-byte granules), by one thread.
 __device__ __forceinline__ void prefetch_slice_l2(const uint8_t* base, long long bytes, int cta, int ctas) {
@@ -222,6 +224,15 @@ __device__ __forceinline__ float gate_fast(const EpilogueArgs& ra, float g, floa
   g = fminf(g, ra.gate_limit);
   u = fminf(fmaxf(u, -ra.gate_limit), ra.gate_limit);
   return g * __frcp_rn(1.0f + __expf(-1.702f * g)) * (u + 1.0f);
+}
+
+// The storing epilogue's activation of one value (EPI_STORE | EPI_GENERAL), uniform over the launch.
+__device__ __forceinline__ float store_act_fast(const EpilogueArgs& ra, float z) {
+  if (ra.gate_act == STORE_RELU2) {
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+  }
+  return 1.0f - 2.0f * __frcp_rn(__expf(2.0f * z) + 1.0f);
 }
 
 // Sums each of sixteen values over the lanes of a warp with sixteen shuffles: at every step a
@@ -628,6 +639,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_c
               sq[j] = 0.f;
               if (row >= rows_m || col >= rows_n) continue;
               float x = v[j];
+              if ((EPI & 7) == EPI_STORE && (EPI & EPI_GENERAL)) x = store_act_fast(ra, x);
               if (ADD) x = (EPI & EPI_GENERAL) ? fmaf(ra.alpha, x, old[ADD ? q * 16 + j : 0]) : x + old[ADD ? q * 16 + j : 0];
               store_value<OT>(out + (size_t)col * ldo + row, x);
               if (emit) {
@@ -785,6 +797,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
 #pragma unroll
       for (int rr = 0; rr < 32; ++rr) {
         float v = turn[rr * 33 + lane];
+        if ((EPI & 7) == EPI_STORE && (EPI & EPI_GENERAL)) v = store_act_fast(ra, v);
         if (ACC) v = (EPI & EPI_GENERAL) ? fmaf(ra.alpha, v, old_cur[ACC ? rr : 0]) : v + old_cur[ACC ? rr : 0];
         if (rr < rows_valid) store_value<OT>(gbase + (size_t)rr * ldo + c, v);
         if (EMIT) {
@@ -955,10 +968,15 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, int row, int n0, O
           for (int j = 0; j < 16; ++j) v[j] = (EPI & EPI_GENERAL) ? fmaf(ra.alpha, v[j], gb::to_float<OT>(p[j])) : v[j] + gb::to_float<OT>(p[j]);
         }
       }
+      if ((EPI & 7) == EPI_STORE && (EPI & EPI_GENERAL)) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = store_act_fast(ra, v[j]);
+      }
       epilogue_store16<OT>(p, v, vec);
     } else {
       for (int j = 0; j < 16 && col + j < rows_n; ++j) {
         float x = v[j];
+        if ((EPI & 7) == EPI_STORE && (EPI & EPI_GENERAL)) x = store_act_fast(ra, x);
         if ((EPI & 7) == EPI_ACCUMULATE) x = (EPI & EPI_GENERAL) ? fmaf(ra.alpha, x, gb::to_float<OT>(p[j])) : x + gb::to_float<OT>(p[j]);
         store_value<OT>(p + j, x);
       }
@@ -1416,6 +1434,8 @@ template <int BN>
 int dispatch_cluster(int epi, int out_dtype, const CUtensorMap& mm, const CUtensorMap& mn, void* out, int ldo,
                      int weight_rows, int out_features, int tokens, int K, cudaStream_t stream, const EpilogueArgs& ra) {
   if ((epi & 7) == EPI_STORE) {
+    if (ra.gate_act >= STORE_RELU2)
+      return launch_cluster<BN, EPI_STORE | EPI_GENERAL, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, ldo, weight_rows, out_features, tokens, K, stream, ra);
     if (out_dtype == GB_F32)
       return launch_cluster<BN, EPI_STORE, float>(mm, mn, (float*)out, ldo, weight_rows, out_features, tokens, K, stream, ra);
     return launch_cluster<BN, EPI_STORE, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, ldo, weight_rows, out_features, tokens, K, stream, ra);
@@ -1601,7 +1621,7 @@ GB_EXPORT int gb_gemm_tc_supported(const void* x, const void* w, int Mx, int Nw,
 // 2: w holds gate and up rows packed in groups of 64 ([128 * ceil(Nw / 64), K], see the head of this
 // file); out[Mx,Nw] (bf16) = act(x gate^T, x up^T), act by gate_act: silu(g) u unless told otherwise.
 // alpha: the accumulating epilogue adds alpha * product. gate_act, gate_limit: the gated epilogue's
-// activation (GateAct).
+// activation (GateAct), or with epi 0 and a bfloat16 output STORE_RELU2 / STORE_TANH: out = act(x w^T).
 GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw, int K, int out_dtype, int epi,
                          const GbNormFold* norm, float alpha, int gate_act, float gate_limit, cudaStream_t stream) {
   if (!gb_gemm_tc_supported(x, w, Mx, Nw, K))
@@ -1614,7 +1634,10 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
   EpilogueArgs ra{};
   fold_norm(ra, norm);
   take_next_stream(ra);
-  if (gate_act < GATE_SILU || gate_act > GATE_CLAMPED_SWISH) return gb::fail(GB_BAD_ARGUMENT, "gemm_tc: gate activation %d", gate_act);
+  if (gate_act < GATE_SILU || gate_act > STORE_TANH) return gb::fail(GB_BAD_ARGUMENT, "gemm_tc: activation %d", gate_act);
+  if (gate_act >= STORE_RELU2 && ((epi & 7) != EPI_STORE || out_dtype != GB_BF16))
+    return gb::fail(GB_BAD_ARGUMENT, "gemm_tc: an activation of one value goes with the storing epilogue and a bfloat16 output");
+  if (gate_act < STORE_RELU2 && (epi & 7) != EPI_SWIGLU) gate_act = GATE_SILU;       // means nothing to the other epilogues
   ra.alpha = alpha;
   ra.gate_act = gate_act;
   ra.gate_limit = gate_limit;
@@ -1647,6 +1670,8 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
       return LAUNCH<BN_, EPI_ACCUMULATE | EPI_GENERAL, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream, ra); \
     if ((epi & 7) == EPI_ACCUMULATE)                                                                                  \
       return LAUNCH<BN_, EPI_ACCUMULATE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream, ra);         \
+    if (ra.gate_act >= STORE_RELU2)                                                                                   \
+      return LAUNCH<BN_, EPI_STORE | EPI_GENERAL, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K, stream, ra); \
     if (out_dtype == GB_F32)                                                                                          \
       return LAUNCH<BN_, EPI_STORE, float>(mm, mn, (float*)out, Nw, Mx, weight_rows, Nw, K, stream, ra);              \
     return LAUNCH<BN_, EPI_STORE, __nv_bfloat16>(mm, mn, (__nv_bfloat16*)out, Nw, Mx, weight_rows, Nw, K, stream, ra); \

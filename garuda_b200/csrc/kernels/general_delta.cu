@@ -11,7 +11,7 @@
 //   gdelta_prepare      a block per token: decays, removal rates, unit keys
 //   gdelta_recurrence   eight threads share a column (every eighth row each, in registers) and
 //                       exchange two sums per token by shuffles; a token's r, u, w, a*u, k come
-//                       through shared memory, four tokens at a time in two buffers
+//                       through shared memory, eight (or four) tokens at a time in two buffers
 //   gdelta_decode       all of it, with the read-out's norm, weight and gate, for steps of one
 //                       token per request: a block per (request, head)
 // The read-out's norm for longer steps is delta_out (delta_rule.cu). A token's result depends on
@@ -56,7 +56,6 @@ gdelta_prepare_kernel(const float* __restrict__ proj, int P, int col_r, int col_
   for (int c = threadIdx.x; c < H * vdim; c += blockDim.x) out[5 * HD + c] = row[col_v + c];
 }
 
-constexpr int CHUNK = 4;
 constexpr int SPLIT = 8;        // threads that share a column of S: thread `sub` holds the rows d with d % 8 == sub
 constexpr int REC_THREADS = 128, REC_COLS = REC_THREADS / SPLIT;
 constexpr int VECS = 5;         // r, u, w, a*u, k
@@ -70,7 +69,7 @@ __device__ __forceinline__ void cp_async_4(float* smem, const float* gmem) {
 // eight sums its rows in ascending order and the eight are added as a tree, ((0 + 1) + (2 + 3)) +
 // ((4 + 5) + (6 + 7)): the same sums, in the same order, as the eight interleaved partial sums of
 // the one-token kernel below. EXACT: dim == MAXD, no row of a thread is beyond the head's.
-template <int MAXD, bool EXACT>
+template <int MAXD, bool EXACT, int CHUNK>
 __global__ void __launch_bounds__(REC_THREADS)
 gdelta_recurrence_kernel(const float* __restrict__ prep, int W, const int32_t* __restrict__ cu_q,
                          const int32_t* __restrict__ slots, float* __restrict__ state, long long state_stride, int H,
@@ -281,11 +280,15 @@ GB_EXPORT int gb_gdelta_recurrence(const float* prep, int W, const int32_t* cu_q
   if (H < 1 || dim < 1 || vdim < 1) return gb::fail(GB_BAD_ARGUMENT, "gdelta_recurrence: sizes");
   const dim3 grid(H, R, (vdim + REC_COLS - 1) / REC_COLS);
   const int per = ((dim + SPLIT - 1) / SPLIT + 3) / 4 * 4 + 4;
-  const size_t smem = (size_t)2 * CHUNK * (VECS * SPLIT * per + REC_COLS + 4) * sizeof(float);   // 47 KB at 256 channels
+  const size_t tok = (size_t)(VECS * SPLIT * per + REC_COLS + 4) * sizeof(float);
+  // eight tokens a round where two buffers of them fit in 48 KB (up to 64 key channels), else four (47 KB at 256)
+  const bool eight = 2 * 8 * tok <= 48 * 1024;
+  const size_t smem = 2 * (eight ? 8 : 4) * tok;
   if (smem > 48 * 1024) return gb::fail(GB_UNSUPPORTED, "gdelta_recurrence: %d key channels per head", dim);
   return by_dim(dim, "gdelta_recurrence", [&](auto maxd) -> int {
     constexpr int MAXD = decltype(maxd)::value;
-    auto kernel = dim == MAXD ? gdelta_recurrence_kernel<MAXD, true> : gdelta_recurrence_kernel<MAXD, false>;
+    auto kernel = eight ? (dim == MAXD ? gdelta_recurrence_kernel<MAXD, true, 8> : gdelta_recurrence_kernel<MAXD, false, 8>)
+                        : (dim == MAXD ? gdelta_recurrence_kernel<MAXD, true, 4> : gdelta_recurrence_kernel<MAXD, false, 4>);
     return gb::check_pdl_launch(gb::launch_pdl(kernel, grid, dim3(REC_THREADS), smem, stream, dim3(1, 1, 1), prep, W, cu_q, slots,
                                                state, state_stride, H, dim, vdim, out),
                                 "gdelta_recurrence");

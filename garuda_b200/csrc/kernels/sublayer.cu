@@ -92,28 +92,45 @@ __device__ __forceinline__ float act(float z, int kind) {
   }
 }
 
-template <typename XT>
-__global__ void gate_mul_kernel(XT* __restrict__ x, const float* __restrict__ gate, int gate_stride, long long total,
-                                int n, int kind) {
+// grid (ceil(n / (4 * 256)), rows): a thread takes four neighbouring values of one row (VEC: rows start on
+// 16 bytes and n is a multiple of four, so the four are one load), else one value at a time.
+template <typename XT, bool VEC>
+__global__ void __launch_bounds__(256)
+gate_mul_kernel(XT* __restrict__ x, const float* __restrict__ gate, int gate_stride, int n, int kind) {
   gb::pdl_launch_dependents();
   gb::pdl_wait();
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const long long t = i / n;
-    const int c = (int)(i % n);
-    x[i] = gb::from_float<XT>(gb::to_float<XT>(x[i]) * act(gate[t * gate_stride + c], kind));
+  const size_t t = blockIdx.y;
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (c0 >= n) return;
+  XT* xr = x + t * n + c0;
+  const float* gr = gate + t * gate_stride + c0;
+  if (VEC) {
+    const float4 g = *reinterpret_cast<const float4*>(gr);
+    const float gs[4] = {g.x, g.y, g.z, g.w};
+    XT v[4];
+    if (sizeof(XT) == 2) *reinterpret_cast<uint2*>(v) = *reinterpret_cast<const uint2*>(xr);
+    else *reinterpret_cast<float4*>(v) = *reinterpret_cast<const float4*>(xr);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = gb::from_float<XT>(gb::to_float<XT>(v[j]) * act(gs[j], kind));
+    if (sizeof(XT) == 2) *reinterpret_cast<uint2*>(xr) = *reinterpret_cast<const uint2*>(v);
+    else *reinterpret_cast<float4*>(xr) = *reinterpret_cast<const float4*>(v);
+  } else {
+    for (int j = 0; j < 4 && c0 + j < n; ++j) xr[j] = gb::from_float<XT>(gb::to_float<XT>(xr[j]) * act(gr[j], kind));
   }
 }
 
 template <typename IT, typename OT>
-__global__ void unary_act_kernel(const IT* __restrict__ z, int z_stride, OT* __restrict__ out, int out_stride,
-                                 long long total, int n, int kind) {
+__global__ void __launch_bounds__(256)
+unary_act_kernel(const IT* __restrict__ z, int z_stride, OT* __restrict__ out, int out_stride, int n, int kind) {
   gb::pdl_launch_dependents();
   gb::pdl_wait();
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const long long t = i / n;
-    const int c = (int)(i % n);
-    out[t * out_stride + c] = gb::from_float<OT>(act(gb::to_float<IT>(z[t * z_stride + c]), kind));
-  }
+  const size_t t = blockIdx.y;
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  const IT* zr = z + t * z_stride + c0;
+  OT* o = out + t * out_stride + c0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (c0 + j < n) o[j] = gb::from_float<OT>(act(gb::to_float<IT>(zr[j]), kind));
 }
 
 constexpr int MAX_BRANCHES = 4;
@@ -123,64 +140,133 @@ struct Branches {
   int n;
 };
 
-__device__ __forceinline__ float block_sum(float v, float* red) {
-  v = gb::warp_sum(v);
+// Sums of up to MAX_BRANCHES values over the block at once; every thread adds the warps' sums in the
+// same order.
+template <int N>
+__device__ __forceinline__ void block_sums(float (&v)[N], float* red) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+#pragma unroll
+  for (int i = 0; i < N; ++i) v[i] = gb::warp_sum(v[i]);
   __syncthreads();                  // `red` may still be read from the call before
-  if (lane == 0) red[warp] = v;
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) red[warp * N + i] = v[i];
+  }
   __syncthreads();
-  float total = 0.f;
-  for (int i = 0; i < warps; ++i) total += red[i];      // every thread adds in the same order
-  return total;
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    float total = 0.f;
+    for (int w = 0; w < warps; ++w) total += red[w * N + i];
+    v[i] = total;
+  }
 }
 
-// One block per token; the row lives in shared memory between the passes.
+// One block per token. A thread owns the channels c with (c / 4) % blockDim.x == threadIdx.x (four
+// neighbours at a time; VEC: as one 16-byte access). Pass 1: every branch's sum of squares. Pass 2: the
+// merged, gated row (kept in shared memory) and its sum of squares. Pass 3: the residual and its rounded copy.
+template <bool VEC>
 __global__ void __launch_bounds__(256)
 sublayer_merge_kernel(Branches br, float alpha, float branch_eps, const float* __restrict__ gate, int gate_stride,
                       const float* __restrict__ gate_bias, const float* __restrict__ w, float eps, float* __restrict__ x,
                       float* __restrict__ out, __nv_bfloat16* __restrict__ rounded, int d) {
-  extern __shared__ float rowbuf[];       // [d]
-  __shared__ float red[8];
+  extern __shared__ __align__(16) float rowbuf[];       // [d rounded up to four]
+  __shared__ float red[8 * MAX_BRANCHES];
   gb::pdl_launch_dependents();
   gb::pdl_wait();
   const size_t t = blockIdx.x;
-  if (br.w[0] != nullptr) {
-    for (int c = threadIdx.x; c < d; c += blockDim.x) rowbuf[c] = 0.f;
-    for (int b = 0; b < br.n; ++b) {
-      const float* y = br.y[b] + t * d;
-      float ss = 0.f;
-      for (int c = threadIdx.x; c < d; c += blockDim.x) ss = fmaf(y[c], y[c], ss);
-      const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + branch_eps);
-      for (int c = threadIdx.x; c < d; c += blockDim.x) rowbuf[c] += (y[c] * inv) * br.w[b][c];
+  const bool merged = br.w[0] != nullptr;
+  auto load4 = [&](const float* p, int c, float (&v)[4]) {
+    if (VEC) {
+      const float4 q = *reinterpret_cast<const float4*>(p + c);
+      v[0] = q.x, v[1] = q.y, v[2] = q.z, v[3] = q.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = c + j < d ? p[c + j] : 0.f;
     }
-    for (int c = threadIdx.x; c < d; c += blockDim.x) rowbuf[c] *= alpha;
-  } else {
-    const float* y = br.y[0] + t * d;
-    for (int c = threadIdx.x; c < d; c += blockDim.x) rowbuf[c] = y[c];
+  };
+  float inv_b[MAX_BRANCHES] = {1.f, 1.f, 1.f, 1.f};
+  if (merged) {
+    float ss[MAX_BRANCHES] = {0.f, 0.f, 0.f, 0.f};
+    for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+#pragma unroll
+      for (int b = 0; b < MAX_BRANCHES; ++b) {
+        if (b >= br.n) break;
+        float v[4];
+        load4(br.y[b] + t * d, c, v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ss[b] = fmaf(v[j], v[j], ss[b]);
+      }
+    }
+    block_sums(ss, red);
+#pragma unroll
+    for (int b = 0; b < MAX_BRANCHES; ++b) inv_b[b] = alpha / sqrtf(ss[b] / (float)d + branch_eps);
   }
-  if (gate != nullptr) {
-    const float* g = gate + t * gate_stride;
-    for (int c = threadIdx.x; c < d; c += blockDim.x)
-      rowbuf[c] *= sigmoidf_(g[c] + (gate_bias ? gate_bias[c] : 0.f));
+  float sq[1] = {0.f};
+  for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+    float y[4] = {0.f, 0.f, 0.f, 0.f};
+    if (merged) {
+#pragma unroll
+      for (int b = 0; b < MAX_BRANCHES; ++b) {
+        if (b >= br.n) break;
+        float v[4], wb[4];
+        load4(br.y[b] + t * d, c, v);
+        load4(br.w[b], c, wb);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) y[j] = fmaf(v[j] * inv_b[b], wb[j], y[j]);
+      }
+    } else {
+      load4(br.y[0] + t * d, c, y);
+    }
+    if (gate != nullptr) {
+      float g[4], gbias[4] = {0.f, 0.f, 0.f, 0.f};
+      if (VEC) load4(gate + t * gate_stride, c, g);
+      else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) g[j] = c + j < d ? gate[t * gate_stride + c + j] : 0.f;
+      }
+      if (gate_bias != nullptr) load4(gate_bias, c, gbias);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) y[j] *= sigmoidf_(g[j] + gbias[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (c + j < d) {
+        if (x == nullptr) out[t * d + c + j] = y[j];
+        else rowbuf[c + j] = y[j];
+        sq[0] = fmaf(y[j], y[j], sq[0]);
+      }
+    }
   }
-  if (x == nullptr) {
-    for (int c = threadIdx.x; c < d; c += blockDim.x) out[t * d + c] = rowbuf[c];
-    return;
-  }
-  float ss = 0.f;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) ss = fmaf(rowbuf[c], rowbuf[c], ss);
-  const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
-  for (int c = threadIdx.x; c < d; c += blockDim.x) {
-    const float v = x[t * d + c] + (rowbuf[c] * inv) * w[c];
-    x[t * d + c] = v;
-    if (rounded != nullptr) rounded[t * d + c] = __float2bfloat16_rn(v);
+  if (x == nullptr) return;
+  block_sums(sq, red);
+  const float inv = 1.0f / sqrtf(sq[0] / (float)d + eps);
+  for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+    float xv[4], wv[4];
+    load4(x + t * d, c, xv);
+    load4(w, c, wv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) xv[j] += (rowbuf[c + j] * inv) * wv[j];      // a thread reads back what it wrote itself
+    if (VEC) {
+      *reinterpret_cast<float4*>(x + t * d + c) = make_float4(xv[0], xv[1], xv[2], xv[3]);
+      if (rounded != nullptr) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(xv[0], xv[1]), hi = __floats2bfloat162_rn(xv[2], xv[3]);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(rounded + t * d + c) = packed;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c + j < d) {
+          x[t * d + c + j] = xv[j];
+          if (rounded != nullptr) rounded[t * d + c + j] = __float2bfloat16_rn(xv[j]);
+        }
+    }
   }
 }
 
-int grid_for(long long total, int block) {
-  long long g = (total + block - 1) / block;
-  return (int)(g > 148 * 32 ? 148 * 32 : (g < 1 ? 1 : g));
-}
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace
 
@@ -208,10 +294,12 @@ GB_EXPORT int gb_gate_mul(void* x, int x_dtype, const float* gate, int gate_stri
                           cudaStream_t stream) {
   if (T <= 0 || n <= 0) return GB_OK;
   if (kind != ACT_SIGMOID && kind != ACT_SILU) return gb::fail(GB_BAD_ARGUMENT, "gate_mul: kind %d", kind);
-  const long long total = (long long)T * n;
+  if (T > 65535) return gb::fail(GB_UNSUPPORTED, "gate_mul: %d rows (at most 65535 a call)", T);
+  const dim3 grid((n + 1023) / 1024, T);
+  const bool vec = n % 4 == 0 && gate_stride % 4 == 0 && aligned16(x) && aligned16(gate);
   return GB_DISPATCH_DTYPE(x_dtype, XT, [&]() -> int {
-    return gb::check_pdl_launch(gb::launch_pdl(gate_mul_kernel<XT>, dim3(grid_for(total, 256)), dim3(256), 0, stream,
-                                               dim3(1, 1, 1), (XT*)x, gate, gate_stride, total, n, kind),
+    auto kernel = vec ? gate_mul_kernel<XT, true> : gate_mul_kernel<XT, false>;
+    return gb::check_pdl_launch(gb::launch_pdl(kernel, grid, dim3(256), 0, stream, dim3(1, 1, 1), (XT*)x, gate, gate_stride, n, kind),
                                 "gate_mul");
   });
 }
@@ -220,11 +308,12 @@ GB_EXPORT int gb_unary_act(const void* z, int z_dtype, int z_stride, void* out, 
                            int kind, cudaStream_t stream) {
   if (T <= 0 || n <= 0) return GB_OK;
   if (kind < ACT_SIGMOID || kind > ACT_TANH) return gb::fail(GB_BAD_ARGUMENT, "unary_act: kind %d", kind);
-  const long long total = (long long)T * n;
+  if (T > 65535) return gb::fail(GB_UNSUPPORTED, "unary_act: %d rows (at most 65535 a call)", T);
+  const dim3 grid((n + 1023) / 1024, T);
   return GB_DISPATCH_DTYPE(z_dtype, IT, [&]() -> int {
     return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
-      return gb::check_pdl_launch(gb::launch_pdl(unary_act_kernel<IT, OT>, dim3(grid_for(total, 256)), dim3(256), 0, stream,
-                                                 dim3(1, 1, 1), (const IT*)z, z_stride, (OT*)out, out_stride, total, n, kind),
+      return gb::check_pdl_launch(gb::launch_pdl(unary_act_kernel<IT, OT>, grid, dim3(256), 0, stream, dim3(1, 1, 1), (const IT*)z,
+                                                 z_stride, (OT*)out, out_stride, n, kind),
                                   "unary_act");
     });
   });
@@ -241,15 +330,20 @@ GB_EXPORT int gb_sublayer_merge(const float* const* ys, const float* const* ws, 
   if ((x == nullptr) == (out == nullptr)) return gb::fail(GB_BAD_ARGUMENT, "sublayer_merge: either x or out");
   if (x != nullptr && w == nullptr) return gb::fail(GB_BAD_ARGUMENT, "sublayer_merge: the norm's weight is missing");
   if (rounded != nullptr && x == nullptr) return gb::fail(GB_BAD_ARGUMENT, "sublayer_merge: a rounded copy is of x");
-  const size_t smem = (size_t)d * sizeof(float);
+  const size_t smem = (size_t)((d + 3) / 4 * 4) * sizeof(float);
   if (smem > 48 * 1024) return gb::fail(GB_UNSUPPORTED, "sublayer_merge: rows of %d (at most 12288)", d);
   Branches br = {};
   br.n = branches;
+  bool vec = d % 4 == 0 && gate_stride % 4 == 0 && aligned16(gate) && aligned16(gate_bias) && aligned16(w) && aligned16(x) &&
+             aligned16(out) && (reinterpret_cast<uintptr_t>(rounded) & 7) == 0;
   for (int b = 0; b < branches; ++b) {
     br.y[b] = ys[b];
     br.w[b] = ws ? ws[b] : nullptr;
+    vec = vec && aligned16(ys[b]) && aligned16(br.w[b]);
   }
-  return gb::check_pdl_launch(gb::launch_pdl(sublayer_merge_kernel, dim3(T), dim3(256), smem, stream, dim3(1, 1, 1), br, alpha,
-                                             branch_eps, gate, gate_stride, gate_bias, w, eps, x, out, (__nv_bfloat16*)rounded, d),
+  const int threads = d >= 1024 ? 256 : 128;
+  auto kernel = vec ? sublayer_merge_kernel<true> : sublayer_merge_kernel<false>;
+  return gb::check_pdl_launch(gb::launch_pdl(kernel, dim3(T), dim3(threads), smem, stream, dim3(1, 1, 1), br, alpha, branch_eps,
+                                             gate, gate_stride, gate_bias, w, eps, x, out, (__nv_bfloat16*)rounded, d),
                               "sublayer_merge");
 }

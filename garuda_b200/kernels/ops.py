@@ -1065,6 +1065,22 @@ class CudaOps:
                                       _tag(out, "activation out"), out.stride(0), T, n, self.UNARY_ACTS[kind],
                                       self._stream()), "activation")
 
+    def linear_act(self, ctx, a, w, out, kind: str):
+        """``out[M,N] = act(a[M,K] @ w[N,K]^T)``, the activation (see ``activation``) in 32-bit on the
+        32-bit sums and rounded once: in the product's epilogue where the tensor-core kernel takes
+        the shape, else a product into a 32-bit row and the activation kernel."""
+        self._on_device(a, w, out)
+        M, K = a.shape
+        N = w.shape[0]
+        _need(w.shape[1] == K and tuple(out.shape) == (M, N) and a.dtype == w.dtype, "linear_act: shapes and dtypes")
+        _need(a.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear_act: operands must be contiguous")
+        _need(kind in self.UNARY_ACTS, f"linear_act: unknown kind {kind!r}")
+        if self.tc is not None and a.dtype == torch.bfloat16 and self.tc.linear_act(a, w, out, kind):
+            return
+        z = ctx.ws.get("linear_act_z", (M, N), torch.float32)
+        self.linear(a, w, z)
+        self.activation(z, out, kind)
+
     def sublayer_merge(self, ys, branch_weights, eps, x=None, out=None, gate=None, gate_bias=None, weight=None,
                        branch_eps=None, rounded=None):
         """What stands between a sublayer's output and the residual where the output, not the input, is

@@ -156,6 +156,15 @@ class TensorCoreKernels:
                             sums_out=emit.sums.data_ptr(), sums_ld=emit.sums.shape[1])
         return self._gemm(a, w, out, w.shape[0], 1 if accumulate else 0, fold, alpha=alpha)
 
+    STORE_ACTS = {"relu2": 3, "tanh": 4}
+
+    def linear_act(self, a, w, out, kind: str) -> bool:
+        """``out = act(a w^T)`` in bfloat16, the activation (``relu2``, ``tanh``) on the 32-bit sums in
+        the product's epilogue."""
+        if w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or kind not in self.STORE_ACTS:
+            return False
+        return self._gemm(a, w, out, w.shape[0], 0, gate_act=self.STORE_ACTS[kind])
+
     def takes_qkv(self, h, w_qkv, q_out, head_dim) -> bool:
         """Whether the fused query/key/value product takes these operands (head sizes that
         divide 128, bfloat16, rows the TMA can address)."""

@@ -123,10 +123,8 @@ class PlainFeedForward(FeedForward):
 
     def forward(self, ctx, h, residual=None):
         T = h.shape[0]
-        z = ctx.ws.get("ffn_up", (T, self.inner), torch.float32)
-        self.ops.linear(h, self.w_up, z)
         act = ctx.ws.get("ffn_act", (T, self.inner), self.dtype)
-        self.ops.activation(z, act, self.activation)
+        self.ops.linear_act(ctx, h, self.w_up, act, self.activation)
         if residual is not None:
             self.ops.linear(act, self.w_down, residual, accumulate=True)
             return None

@@ -394,6 +394,9 @@ class CpuOps:
     def activation(self, z, out, kind):
         out.copy_(self._unary(z.float(), kind).to(out.dtype))
 
+    def linear_act(self, ctx, a, w, out, kind):
+        out.copy_(self._unary(a.float() @ w.float().t(), kind).to(out.dtype))
+
     def sublayer_merge(self, ys, branch_weights, eps, x=None, out=None, gate=None, gate_bias=None, weight=None,
                        branch_eps=None, rounded=None):
         """y = mean_b rms(y_b) w_b (or the one y); y *= sigmoid(gate + bias); x += rms(y) weight (or out = y)"""
