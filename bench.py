@@ -1022,12 +1022,11 @@ def run_design_luvapel(args) -> dict:
             h = torch.randn(M, W, device=dev).to(bf)
             x = torch.zeros(M, W, device=dev)
             up, dwn = (torch.randn(FF, W, device=dev) * 0.02).to(bf), (torch.randn(W, FF, device=dev) * 0.02).to(bf)
-            zbuf, act = torch.empty(M, FF, device=dev), torch.empty(M, FF, dtype=bf, device=dev)
+            act, y = torch.empty(M, FF, dtype=bf, device=dev), torch.empty(M, W, device=dev)
 
             def plain():
-                ops.linear(h, up, zbuf)
-                ops.activation(zbuf, act, "relu2")
-                ops.linear(act, dwn, x, accumulate=True)
+                ops.linear_act(ctx, h, up, act, "relu2")
+                ops.linear(act, dwn, y)
 
             kern[f"relu2_feed_forward_{label}"] = roof(timed(plain), 2.0 * M * 2 * FF * W, 2.0 * 2 * FF * W)
             g = ops.pack_gate_up((torch.randn(FF, W, device=dev) * 0.02).to(bf), (torch.randn(FF, W, device=dev) * 0.02).to(bf))
@@ -1037,7 +1036,7 @@ def run_design_luvapel(args) -> dict:
                 ops.linear(act, dwn, x, accumulate=True)
 
             kern[f"llama_silu_feed_forward_{label}"] = roof(timed(dense), 2.0 * M * 3 * FF * W, 2.0 * 3 * FF * W)
-            del up, dwn, g, zbuf, act
+            del up, dwn, g, y, act
         # the recurrent mixers: bytes are their rows in and out and the state
 
         class Bt:

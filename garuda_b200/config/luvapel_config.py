@@ -3,7 +3,7 @@
 Keys: ``architecture`` ("Luvapel"), ``vocab``, ``width``, ``embedding.scale``,
 ``norm.eps``, ``layers`` (a list; each entry has ``type`` = ``parallel`` |
 ``general_delta``, the mixer's sizes under ``mixer``, its feed-forward under
-``mlp`` or null, and optionally ``weights_of``: the index of an earlier layer
+``mlp`` or null, and optionally ``weights_of``: the index of another layer
 whose tensors this layer runs with, keeping a cache and a state of its own),
 ``max_positions`` (optional: the longest sequence; the design itself has no
 limit).
@@ -149,11 +149,21 @@ class LuvapelConfig:
             src = e.get("weights_of")
             if src is not None:
                 src = _get(e, "weights_of", w, int, 0)
-                if src >= i or layers[src].weights_of is not None:
-                    raise ConfigError(f"config.json: '{w}weights_of' = {src} must name an earlier layer with tensors of its own")
-                if (layers[src].type, layers[src].mixer, layers[src].mlp) != (kind, mixer, mlp):
-                    raise ConfigError(f"config.json: layer {i} runs with the tensors of layer {src} but its sizes differ")
+                if src >= len(entries) or src == i:
+                    raise ConfigError(f"config.json: '{w}weights_of' = {src} must name another layer")
             layers.append(LuvapelLayer(kind, mixer, mlp, src))
+        for i, layer in enumerate(layers):
+            # a layer may name one that names another: follow to the layer that has the tensors
+            src, seen = layer.weights_of, {i}
+            while src is not None and layers[src].weights_of is not None:
+                if src in seen:
+                    raise ConfigError(f"config.json: 'layers[{i}].weights_of' leads back to itself")
+                seen.add(src)
+                src = layers[src].weights_of
+            if src is not None:
+                if (layers[src].type, layers[src].mixer, layers[src].mlp) != (layer.type, layer.mixer, layer.mlp):
+                    raise ConfigError(f"config.json: layer {i} runs with the tensors of layer {src} but its sizes differ")
+                layers[i] = LuvapelLayer(layer.type, layer.mixer, layer.mlp, src)
         eos = d.get("eos_token_id")
         eos = () if eos is None else tuple(eos) if isinstance(eos, (list, tuple)) else (int(eos),)
         return cls(architecture=d.get("architecture", "Luvapel"), vocab=vocab, width=width, embedding_scale=scale,

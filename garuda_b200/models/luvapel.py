@@ -40,10 +40,9 @@ def _mixer(cfg, layer, p):
 
 
 def luvapel_spec(cfg: LuvapelConfig) -> ModelSpec:
-    layers, order, ignored, at = [], [], [], {}
+    layers, ignored, at = [], [], {}
     for i, layer in enumerate(cfg.layers):
         if layer.weights_of is not None:
-            order.append(LayerCall(at[layer.weights_of]))       # the same tensors, a cache and a state of its own
             continue
         p = f"l{i}."
         ff = None
@@ -57,7 +56,8 @@ def luvapel_spec(cfg: LuvapelConfig) -> ModelSpec:
                                 feed_forward_norm=_norm(cfg, p, "norm2") if ff is not None else None,
                                 arrangement="sublayer_norm", mixer_gate=gate("rg1"),
                                 feed_forward_gate=gate("rg2") if ff is not None else None))
-        order.append(LayerCall(at[i]))
+    # a layer that names another runs that layer's block again, with a cache and a state of its own
+    order = [LayerCall(at[i if layer.weights_of is None else layer.weights_of]) for i, layer in enumerate(cfg.layers)]
     return ModelSpec(
         architecture=cfg.architecture, width=cfg.width, vocab_size=cfg.vocab, max_positions=cfg.max_positions,
         embedding="embed", layers=layers, order=order, final_norm=_norm(cfg, "", "final.norm"), head="head",

@@ -149,8 +149,10 @@ def forward(config, weights, tokens, layers_out=None):
     eps = config["norm"]["eps"]
     x = W["embed"][np.asarray(tokens)] * config["embedding"]["scale"]
     for i, layer in enumerate(config["layers"]):
-        src = layer.get("weights_of")
-        p = f"l{i if src is None else src}."
+        src = i
+        while config["layers"][src].get("weights_of") is not None:       # the layer that has the tensors
+            src = config["layers"][src]["weights_of"]
+        p = f"l{src}."
         y = MIXERS[layer["type"]](W, p + "mix.", x, layer["mixer"], eps)
         y = y * sigmoid(x @ W[p + "rg1"].T + W[p + "rg1.b"])
         x = x + rms(y, eps) * W[p + "norm1"]

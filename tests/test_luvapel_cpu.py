@@ -155,9 +155,39 @@ def test_configuration_errors_name_the_key():
     with pytest.raises(ConfigError, match="sizes differ"):
         read_model_config(bad)
     bad = json.loads(json.dumps(LA))
-    bad["layers"][4]["weights_of"] = 2
-    with pytest.raises(ConfigError, match="tensors of its own"):
+    bad["layers"][4]["weights_of"] = 2                 # through layer 2 to layer 0, which is of the other kind
+    with pytest.raises(ConfigError, match="sizes differ"):
         read_model_config(bad)
+    for i, j, text in ((2, 2, "another layer"), (2, 9, "another layer")):
+        bad = json.loads(json.dumps(LA))
+        bad["layers"][i]["weights_of"] = j
+        with pytest.raises(ConfigError, match=text):
+            read_model_config(bad)
+    bad = json.loads(json.dumps(LA))
+    bad["layers"][0]["weights_of"] = 2
+    with pytest.raises(ConfigError, match="back to itself"):
+        read_model_config(bad)
+
+
+def test_a_layer_may_name_a_later_layer_or_one_that_names_another(tmp_path):
+    """The tensors are those of layer 2 alone: layer 0 names it, and layer 3 names layer 0."""
+    from garuda_b200.weights import write_random_model
+    from tests.helpers import folder_weights
+    from tests.luvapel_cases import SHARPEN
+    gd = {"type": "general_delta", "mixer": {"heads": 2, "dim": 8, "decay_rank": 3}, "mlp": {"kind": "dense", "ff": 24}}
+    cfg = {"architecture": "Luvapel", "vocab": 61, "width": 24, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-5},
+           "layers": [dict(gd, weights_of=2), dict(LD["layers"][0]), gd, dict(gd, weights_of=0)]}
+    cfg["layers"][1]["mixer"] = json.loads(json.dumps(LD["layers"][0]["mixer"]))
+    _, model = build_model(cfg)
+    assert [c.layer for c in model.spec.order] == [1, 0, 1, 1] and len(model.blocks) == 2
+    assert not any(n.startswith(("l0.", "l3.")) for n in model.expected_tensors())
+    d = write_random_model(str(tmp_path / "m"), cfg, 3, scale=SHARPEN)
+    toks = np.random.default_rng(0).integers(0, 61, 30).tolist()
+    ref = lp.forward(cfg, folder_weights(d), toks)
+    e = Engine(d, dtype="float32", ops=CpuOps(), cuda_graphs=False, page_size=8, kv_tokens=128, context=64)
+    got = e.step([StepEntry(1, toks[:17], range(17))]).numpy().copy()      # the next step writes the same buffer
+    got = np.concatenate([got, e.step([StepEntry(1, toks[17:], range(13))]).numpy()])
+    assert_close(got, ref, "float32", "layers that name other layers")
 
 
 def test_run_order_and_cache_needs_come_from_the_configuration():
