@@ -110,8 +110,8 @@ inline bool pdl_enabled() {
 // Launch with the programmatic-serialization attribute, and as clusters of the given shape if it
 // holds more than one CTA.
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                              dim3 cluster, Args... args) {
+inline cudaError_t launch_with(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               dim3 cluster, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -119,7 +119,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
   int n = 0;
-  if (pdl_enabled()) {
+  if (early && pdl_enabled()) {
     attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;
@@ -134,6 +134,22 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   cfg.attrs = attrs;
   cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              dim3 cluster, Args... args) {
+  return launch_with(true, kernel, grid, block, smem, stream, cluster, args...);
+}
+
+// The ordinary launch: the kernel starts when the one before it in the stream has finished. For a
+// kernel of few, long-running blocks: started early, its blocks go to whichever SMs have room
+// while the predecessor's still run, several to an SM, and stay there for the kernel's whole time
+// (the generalized delta rule's recurrence, 128 blocks: 1.9 ms started early, 0.78 ms started after).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_after(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                dim3 cluster, Args... args) {
+  return launch_with(false, kernel, grid, block, smem, stream, cluster, args...);
 }
 
 inline int check_pdl_launch(cudaError_t e, const char* what) {

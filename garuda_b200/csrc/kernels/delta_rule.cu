@@ -132,7 +132,6 @@ __global__ void __launch_bounds__(REC_THREADS)
 delta_recurrence_kernel(const float* __restrict__ prep, int W, const int32_t* __restrict__ cu_q,
                         const int32_t* __restrict__ slots, float* __restrict__ state, long long state_stride, int H,
                         int G, int dim, int vdim, float* __restrict__ out) {
-  gb::pdl_launch_dependents();
   gb::pdl_wait();
   constexpr int MINE = MAXD / SPLIT;
   extern __shared__ __align__(16) float stage[];      // 2 x [CHUNK][3 SPLIT per + 32 + 4]
@@ -233,6 +232,8 @@ delta_recurrence_kernel(const float* __restrict__ prep, int W, const int32_t* __
     }
     __syncthreads();
   }
+  // only now may the next kernel in the stream start: its blocks would wait beside these for the whole walk
+  gb::pdl_launch_dependents();
   if (S_g != nullptr) {
 #pragma unroll
     for (int i = 0; i < MINE; ++i) {
@@ -428,7 +429,7 @@ GB_EXPORT int gb_delta_recurrence(const float* prep, int W, const int32_t* cu_q,
     }
     constexpr int MAXD = decltype(maxd)::value;
     auto kernel = dim == MAXD ? delta_recurrence_kernel<MAXD, true> : delta_recurrence_kernel<MAXD, false>;
-    return gb::check_pdl_launch(gb::launch_pdl(kernel, grid, dim3(threads), smem, stream, dim3(1, 1, 1), prep, W, cu_q,
+    return gb::check_pdl_launch(gb::launch_after(kernel, grid, dim3(threads), smem, stream, dim3(1, 1, 1), prep, W, cu_q,
                                                slots, state, state_stride, H, G, dim, vdim, out),
                                 "delta_recurrence");
   });

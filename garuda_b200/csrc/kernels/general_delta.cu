@@ -74,7 +74,6 @@ __global__ void __launch_bounds__(REC_THREADS)
 gdelta_recurrence_kernel(const float* __restrict__ prep, int W, const int32_t* __restrict__ cu_q,
                          const int32_t* __restrict__ slots, float* __restrict__ state, long long state_stride, int H,
                          int dim, int vdim, float* __restrict__ out) {
-  gb::pdl_launch_dependents();
   gb::pdl_wait();
   constexpr int MINE = MAXD / SPLIT;
   extern __shared__ __align__(16) float stage[];      // 2 x [CHUNK][VECS SPLIT per + 16 + 4]
@@ -166,6 +165,8 @@ gdelta_recurrence_kernel(const float* __restrict__ prep, int W, const int32_t* _
     }
     __syncthreads();
   }
+  // only now may the next kernel in the stream start: its blocks would wait beside these for the whole walk
+  gb::pdl_launch_dependents();
   if (S_g != nullptr) {
 #pragma unroll
     for (int i = 0; i < MINE; ++i) {
@@ -289,7 +290,7 @@ GB_EXPORT int gb_gdelta_recurrence(const float* prep, int W, const int32_t* cu_q
     constexpr int MAXD = decltype(maxd)::value;
     auto kernel = eight ? (dim == MAXD ? gdelta_recurrence_kernel<MAXD, true, 8> : gdelta_recurrence_kernel<MAXD, false, 8>)
                         : (dim == MAXD ? gdelta_recurrence_kernel<MAXD, true, 4> : gdelta_recurrence_kernel<MAXD, false, 4>);
-    return gb::check_pdl_launch(gb::launch_pdl(kernel, grid, dim3(REC_THREADS), smem, stream, dim3(1, 1, 1), prep, W, cu_q, slots,
+    return gb::check_pdl_launch(gb::launch_after(kernel, grid, dim3(REC_THREADS), smem, stream, dim3(1, 1, 1), prep, W, cu_q, slots,
                                                state, state_stride, H, dim, vdim, out),
                                 "gdelta_recurrence");
   });
