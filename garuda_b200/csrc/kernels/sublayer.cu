@@ -45,6 +45,9 @@ qk_norm_rope_append_kernel(const float* __restrict__ src, int row_stride, int q_
   __syncthreads();
   const float* row = src + (size_t)t * row_stride;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  // every head of the row starts on 8 bytes (the head width is even)
+  const bool paired = interleaved && ((row_stride | q_col | k_col) & 1) == 0 && (reinterpret_cast<uintptr_t>(src) & 7) == 0 &&
+                      ((reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_pool)) & (2 * sizeof(OT) - 1)) == 0;
   for (int head = warp; head < Hq + Hkv; head += warps) {
     const bool is_q = head < Hq;
     if (!is_q && cache_row < 0) continue;
@@ -59,6 +62,19 @@ qk_norm_rope_append_kernel(const float* __restrict__ src, int row_stride, int q_
     }
     OT* dst = is_q ? q_out + ((size_t)t * Hq + head) * dim
                    : k_pool + ((cache_row + (head - Hq)) * page_size + (pos % page_size)) * dim;
+    if (paired) {        // neighbours rotate together: one 8-byte load and one store for the two
+      for (int i = lane; i < half; i += 32) {
+        const float2 ab = *reinterpret_cast<const float2*>(s + 2 * i);
+        float a = ab.x, b = ab.y;
+        if (normed) a = (a * inv) * w[2 * i], b = (b * inv) * w[2 * i + 1];
+        if (rotate) {
+          const float ra = a * cos_s[i] - b * sin_s[i], rb = b * cos_s[i] + a * sin_s[i];
+          a = ra, b = rb;
+        }
+        gb::store_pair(dst + 2 * i, a, b);
+      }
+      continue;
+    }
     for (int i = lane; i < half; i += 32) {
       const int ia = interleaved ? 2 * i : i;
       const int ib = interleaved ? 2 * i + 1 : i + half;

@@ -74,15 +74,19 @@ def step_batch(lens, slots):
 # ---------------------------------------------------------------------------- kernels
 @pytest.mark.parametrize("Hq,Hkv,dim,rot,values", [(4, 2, 16, 8, "keys"), (3, 3, 24, 24, "keys"), (8, 2, 64, 64, "keys"),
                                                    (2, 1, 128, 32, "projected"), (6, 2, 40, 0, "keys"), (1, 1, 256, 2, "projected")])
-def test_normed_rotated_queries_and_keys_into_pages(both, Hq, Hkv, dim, rot, values):
+@pytest.mark.parametrize("first", [5, 8])
+def test_normed_rotated_queries_and_keys_into_pages(both, Hq, Hkv, dim, rot, values, first):
+    """``first`` = 5: heads that start on odd columns; 8: every head on an even column of rows of even
+    length, where the kernel loads and stores a rotated pair at once."""
     from garuda_b200.parts.attention import NormedKeyAttention
     ops, cpu, dt = both
     ps, T, vdim = 8, 11, dim if values == "keys" else 24
     part = NormedKeyAttention(64, Hq, Hkv, dim, rot_base=300.0 if rot else None, rot_dims=rot, values=values, vdim=vdim)
     rotary = part.rotary
-    cq, ck = 5, 5 + Hq * dim                                  # columns that do not start the row
+    cq, ck = first, first + Hq * dim                          # columns that do not start the row
     cv = ck if values == "keys" else ck + Hkv * dim + 3
-    src = rnd(T, cv + Hkv * vdim + 7, scale=2.0)
+    width = cv + Hkv * vdim + 7
+    src = rnd(T, width + (width + first) % 2, scale=2.0)
     qw, kw = rnd(Hq, dim, seed=1) + 1.0, rnd(dim, seed=2) + 1.0
     pos = torch.tensor([5, 6, 7, 8, 9, 0, 3000, 3001, 3002, 3003, 2], dtype=torch.int32)
     req = torch.tensor([0, 0, 0, 0, 0, 1, 2, 2, 2, 2, 3], dtype=torch.int32)
