@@ -282,7 +282,7 @@ GB_EXPORT int gb_gdelta_recurrence(const float* prep, int W, const int32_t* cu_q
   const dim3 grid(H, R, (vdim + REC_COLS - 1) / REC_COLS);
   const int per = ((dim + SPLIT - 1) / SPLIT + 3) / 4 * 4 + 4;
   const size_t tok = (size_t)(VECS * SPLIT * per + REC_COLS + 4) * sizeof(float);
-  // eight tokens a round where two buffers of them fit in 48 KB (up to 64 key channels), else four (47 KB at 256)
+  // eight tokens at a time where two buffers of them fit in 48 KB (up to 64 key channels), else four (47 KB at 256)
   const bool eight = 2 * 8 * tok <= 48 * 1024;
   const size_t smem = 2 * (eight ? 8 : 4) * tok;
   if (smem > 48 * 1024) return gb::fail(GB_UNSUPPORTED, "gdelta_recurrence: %d key channels per head", dim);
