@@ -185,6 +185,8 @@ delta_recurrence_kernel(const float* __restrict__ prep, int W, const int32_t* __
     asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
     const float* cur = stage + (size_t)buf * CHUNK * tok_floats;
+    // unrolled: a token's read-out (its sum and shuffles) is off the path to the next token's state and overlaps it
+#pragma unroll 4
     for (int tt = 0; tt < n; ++tt) {
       const float* tok = cur + tt * tok_floats;
       const float* sq = tok + sub * per;
