@@ -42,6 +42,8 @@ def replay(engine, lines: Iterable[str], out_dir: str, report=None) -> int:
         step = rec["step"]
         entries = []
         for e in rec.get("entries", []):
+            if not e.get("tokens"):
+                continue            # an entry that brings no tokens leaves its request where it is
             if e["id"] not in ids:
                 ids[e["id"]] = next_id
                 next_id += 1

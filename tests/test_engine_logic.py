@@ -199,7 +199,7 @@ def test_generation_with_a_timeout_ends_the_request_and_frees_what_it_held():
 def test_trace_replay_loop_writes_the_plain_models_logits(tmp_path):
     """The loop behind bin/trace_run, `garuda replay` and Engine.replay, over the reference kernels:
     requests named by strings or numbers, one left out of a step and going on later, blank lines, a
-    step that only ends requests, an unknown name in `end`, pages used again."""
+    step that only ends requests, an unknown name in `end`, an entry without tokens, pages used again."""
     import json
     from garuda_b200.engine.replay import replay
     e = engine("B", kv_tokens=96, max_concurrent=3)           # 12 pages of 8 for 40 + 30 + 33 tokens in turn
@@ -207,7 +207,8 @@ def test_trace_replay_loop_writes_the_plain_models_logits(tmp_path):
     refs = {k: plain_logits("B", torch.float32, t) for k, t in (("a", a), ("b", b), ("c", c))}
     steps = [
         {"step": 0, "entries": [{"id": "a", "tokens": a[:17], "want": [0, 16]}, {"id": 7, "tokens": b[:2], "want": []}], "end": []},
-        {"step": 1, "entries": [{"id": "a", "tokens": a[17:39], "want": [21]}], "end": []},          # 7 sits this one out
+        # 7 sits this one out, once by its absence and once (as "z", not yet begun) with an entry without tokens
+        {"step": 1, "entries": [{"id": "a", "tokens": a[17:39], "want": [21]}, {"id": "z", "tokens": [], "want": []}], "end": []},
         {"step": 2, "entries": [{"id": 7, "tokens": b[2:], "want": [0, 27]}, {"id": "a", "tokens": a[39:], "want": [0]}], "end": ["a", "nobody"]},
         {"step": 3, "entries": [], "end": [7]},
         {"step": 5, "entries": [{"id": "c", "tokens": c, "want": [32]}], "end": ["c"]},
