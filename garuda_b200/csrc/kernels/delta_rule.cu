@@ -393,8 +393,17 @@ GB_EXPORT int gb_delta_prepare(const float* proj, int P, const float* second, in
   if (P < C + H || P2 < (per_head ? H : H * dim) || W != C + H * dim + H)
     return gb::fail(GB_BAD_ARGUMENT, "delta_prepare: row widths");
   const size_t smem = (size_t)C * sizeof(float);
-  if (smem > 48 * 1024) return gb::fail(GB_UNSUPPORTED, "delta_prepare: %d convolved channels", C);
+  constexpr size_t kMostSmem = 224 * 1024;      // what a block may ask for on this GPU, less some for the driver
+  if (smem > kMostSmem) return gb::fail(GB_UNSUPPORTED, "delta_prepare: %d convolved channels (at most %d)", C, (int)(kMostSmem / 4));
   return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
+    if (smem > 48 * 1024) {                      // beyond the default limit a kernel has to ask once
+      static size_t granted = 0;                 // per weight type: this lambda is instantiated for each
+      if (smem > granted) {
+        const cudaError_t e = cudaFuncSetAttribute(delta_prepare_kernel<WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMostSmem);
+        if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "delta_prepare: %s", cudaGetErrorString(e));
+        granted = kMostSmem;
+      }
+    }
     return gb::check_pdl_launch(
         gb::launch_pdl(delta_prepare_kernel<WT>, dim3(T), dim3(256), smem, stream, dim3(1, 1, 1), proj, P, second, P2,
                        (const WT*)conv_w, taps, conv_state, conv_stride, (const WT*)a_log, (const WT*)dt_bias, token_req,

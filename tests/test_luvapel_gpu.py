@@ -153,11 +153,11 @@ def test_branches_gate_norm_and_sum_in_one_pass(T, d, branches):
 
 
 @pytest.mark.parametrize("H,G,dim,vdim,taps", [(4, 2, 12, 20, 3), (1, 1, 40, 36, 1), (4, 2, 32, 64, 4), (2, 1, 128, 128, 2),
-                                               (3, 1, 72, 200, 5)])
+                                               (3, 1, 72, 200, 5), (50, 2, 32, 256, 2)])
 def test_delta_rule_with_one_decay_per_head(both, H, G, dim, vdim, taps):
     """Three steps over the same slots: a mixed step, a step of single tokens only (the fused
     kernel) and another mixed one; decay logits per head and the gate's SiLU, read as column ranges
-    of one wider row."""
+    of one wider row. The last case has more convolved channels (12,928) than 48 KB of shared memory hold."""
     ops, cpu, dt = both
     C = 2 * G * dim + H * vdim
     n_state = H * dim * vdim + (taps - 1) * C
