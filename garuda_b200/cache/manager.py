@@ -44,7 +44,8 @@ class PagedCache:
             raise ValueError("the cache needs num_pages or max_tokens")
         self.groups = model.cache_groups
         self.manager = host.CacheManager(
-            [host.GroupConfig(pages, g.need.window or 0, getattr(g.need, "keep_first", 0) or 0) for g in self.groups],
+            [host.GroupConfig(pages, g.need.window or 0, getattr(g.need, "keep_first", 0) or 0,
+                              getattr(g.need, "chunk", 0) or 0) for g in self.groups],
             ps, config.max_requests, config.max_positions)
         self.page_size = ps
         self.table_width = self.manager.max_pages_per_request

@@ -39,6 +39,9 @@ KERNEL_LIBS: Dict[str, List[str]] = {
     # a residual of several streams, the recurrent delta-rule mixer, keys and values of unequal
     # widths stored with a bias: built when a model first uses them
     "garuda_state": ["streams.cu", "delta_rule.cu", "general_delta.cu", "sublayer.cu"],
+    # a norm after the sum, a gated recurrence per channel, a short convolution in front of attention:
+    # built when a model first uses them
+    "garuda_seq": ["post_norm.cu", "mingru.cu", "conv_qkv.cu"],
 }
 HOST_SOURCES = ["cache_manager.cpp", "scheduler.cpp", "step_batch.cpp", "bindings.cpp"]
 

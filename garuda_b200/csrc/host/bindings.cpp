@@ -53,17 +53,19 @@ PYBIND11_MODULE(_garuda_host, m) {
   py::register_exception<Busy>(m, "Busy", m.attr("SchedulerError").ptr());
 
   py::class_<GroupConfig>(m, "GroupConfig")
-      .def(py::init([](int num_pages, int window, int keep_first) {
+      .def(py::init([](int num_pages, int window, int keep_first, int chunk) {
              GroupConfig g;
              g.keep_first = keep_first;
+             g.chunk = chunk;
              g.num_pages = num_pages;
              g.window = window;
              return g;
            }),
-           py::arg("num_pages"), py::arg("window") = 0, py::arg("keep_first") = 0)
+           py::arg("num_pages"), py::arg("window") = 0, py::arg("keep_first") = 0, py::arg("chunk") = 0)
       .def_readwrite("num_pages", &GroupConfig::num_pages)
       .def_readwrite("window", &GroupConfig::window)
-      .def_readwrite("keep_first", &GroupConfig::keep_first);
+      .def_readwrite("keep_first", &GroupConfig::keep_first)
+      .def_readwrite("chunk", &GroupConfig::chunk);
 
   py::class_<CacheManager>(m, "CacheManager")
       .def(py::init<std::vector<GroupConfig>, int, int, int>(), py::arg("groups"), py::arg("page_size"),

@@ -19,6 +19,8 @@ CacheManager::CacheManager(std::vector<GroupConfig> groups, int page_size, int m
     if (g.num_pages < 0) throw CacheError("a group cannot have a negative number of pages");
     if (g.window < 0) throw CacheError("a window cannot be negative");
     if (g.keep_first < 0) throw CacheError("the number of kept first positions cannot be negative");
+    if (g.chunk < 0) throw CacheError("a chunk cannot be negative");
+    if (g.chunk > 0 && (g.window > 0 || g.keep_first > 0)) throw CacheError("a chunked group takes no window");
     Pool pool;
     pool.free.reserve(g.num_pages);
     // Highest id at the bottom, so that page 0 is handed out first.
@@ -41,6 +43,9 @@ CacheManager::Request& CacheManager::get(int64_t request) {
 }
 
 int CacheManager::first_live_position(int group, int len) const {
+  const int chunk = groups_[group].chunk;
+  // The next query sits at position `len` and reads its own stretch up to itself.
+  if (chunk > 0) return len / chunk * chunk;
   const int w = groups_[group].window;
   if (w <= 0) return 0;
   // The next query sits at position `len` and reads [len + 1 - w, len].
@@ -121,7 +126,7 @@ void CacheManager::commit(int64_t request, int new_len) {
                      " positions but only " + std::to_string(r.reserved) + " are backed by pages");
   r.len = new_len;
   for (size_t g = 0; g < groups_.size(); ++g) {
-    if (groups_[g].window <= 0) continue;
+    if (groups_[g].window <= 0 && groups_[g].chunk <= 0) continue;
     const int first = first_live_page(static_cast<int>(g), r.len);
     for (int p = kept_pages(static_cast<int>(g)); p < first && p < max_pages_; ++p) {
       if (r.tables[g][p] >= 0) {

@@ -6,9 +6,9 @@
 // and by how many sequences run. Here all requests draw pages from one pool per
 // group of layers, and a request's block table says which page holds which
 // stretch of its positions. A group is a set of layers with the same needs
-// (all keys, or a window of them: garuda/src/cache/mod.rs:333-338); groups have
-// pages of their own because a windowed group gives pages back while the
-// request is still running.
+// (all keys, a window of them: garuda/src/cache/mod.rs:333-338, or the keys of
+// the query's own stretch of positions); groups have pages of their own because
+// a windowed or chunked group gives pages back while the request is still running.
 //
 // Only numbers live here. The device memory behind the pages belongs to the
 // Python side, which indexes it with the page ids handed out below.
@@ -35,6 +35,9 @@ struct GroupConfig {
   int num_pages = 0;   // pages in this group's pool
   int window = 0;      // positions a query looks back over, itself included; 0: everything
   int keep_first = 0;  // with a window: the first positions of a request that every query still reads
+  // instead of a window: a query at position i reads the positions of its own stretch of `chunk`,
+  // floor(i / chunk) * chunk .. i; the stretches in front are dead once a query has passed them
+  int chunk = 0;
 };
 
 class CacheManager {

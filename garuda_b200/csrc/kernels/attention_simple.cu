@@ -13,7 +13,11 @@
 // Options that other designs use, each off at its neutral value: `softcap` c > 0 replaces a score
 // by c tanh(s / c) (after the scale); `keep_first` n > 0 lets a windowed query also read the first
 // n positions of its request (at their true positions); `sink` adds one to the softmax's
-// denominator, an entry of score zero that carries no value: p_j = exp(s_j) / (1 + sum exp(s_k)).
+// denominator, an entry of score zero that carries no value: p_j = exp(s_j) / (1 + sum exp(s_k));
+// `sink_v` (one learned number per query head) adds exp(sink_v[h]) there instead, unscaled; `r1`, `r2`
+// (per query head) take r1 ln(1 + r2 (i - j)) off the score of key j for the query at i; `chunk` n > 0
+// lets a query read only the keys of its own stretch of n positions, floor(j / n) = floor(i / n),
+// counted from the request's first position.
 #include "common.cuh"
 
 namespace {
@@ -30,7 +34,8 @@ attention_simple_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, c
                         const int32_t* __restrict__ cu_q, const int32_t* __restrict__ kv_lens,
                         const int32_t* __restrict__ token_req, T* __restrict__ out, int Hq, int Hkv, int hd,
                         int v_hd, int vd, float scale, int window, int page_size, float softcap, int keep_first,
-                        int sink) {
+                        int sink, const float* __restrict__ sink_v, const float* __restrict__ r1,
+                        const float* __restrict__ r2, int chunk) {
   __shared__ float q_s[WARPS][MAX_HD];
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -39,7 +44,8 @@ attention_simple_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, c
   const int r = token_req[t];
   const int q_len = cu_q[r + 1] - cu_q[r];
   const int pos = kv_lens[r] - q_len + (t - cu_q[r]);
-  const int start = window > 0 ? max(0, pos + 1 - window) : 0;
+  const int start = chunk > 0 ? (pos / chunk) * chunk : window > 0 ? max(0, pos + 1 - window) : 0;
+  const float far1 = r1 ? r1[h] : 0.f, far2 = r2 ? r2[h] : 0.f;
   const int kvh = h / (Hq / Hkv);
   const int32_t* table = block_table + (size_t)r * table_width;
 
@@ -75,6 +81,7 @@ attention_simple_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, c
       for (int c = 0; c < hd; ++c) dot = fmaf(q_s[warp][c], gb::to_float<T>(kr[c]), dot);
       s = dot * scale;
       if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+      if (r1) s -= far1 * log1pf(far2 * (float)(pos - j));
     }
     const float m_new = fmaxf(m, gb::warp_max(s));
     if (m_new == -INFINITY) continue;          // a block without a single stored key
@@ -97,7 +104,8 @@ attention_simple_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, c
       }
     }
   }
-  if (sink && m != -INFINITY) l += expf(-m);
+  if (sink_v && m != -INFINITY) l += expf(sink_v[h] - m);
+  else if (sink && m != -INFINITY) l += expf(-m);
   const float inv = l > 0.f ? 1.0f / l : 0.f;
   T* o = out + ((size_t)t * Hq + h) * vd;
 #pragma unroll
@@ -115,7 +123,8 @@ GB_EXPORT int gb_attention_simple(const void* q, const void* k_pool, const void*
                                   const int32_t* block_table, int table_width, const int32_t* cu_q,
                                   const int32_t* kv_lens, const int32_t* token_req, void* out, int T,
                                   int Hq, int Hkv, int hd, int v_hd, int vd, float scale, int window,
-                                  int page_size, float softcap, int keep_first, int sink, cudaStream_t stream) {
+                                  int page_size, float softcap, int keep_first, int sink, const float* sink_v,
+                                  const float* r1, const float* r2, int chunk, cudaStream_t stream) {
   if (T <= 0) return GB_OK;
   constexpr int WIDEST = 1024;
   if (hd > WIDEST || hd < 1)
@@ -123,16 +132,19 @@ GB_EXPORT int gb_attention_simple(const void* q, const void* k_pool, const void*
   if (vd < 1 || vd > v_hd || vd > WIDEST)
     return gb::fail(GB_BAD_ARGUMENT, "attention: %d value channels of rows %d wide", vd, v_hd);
   if (Hkv < 1 || Hq % Hkv) return gb::fail(GB_BAD_ARGUMENT, "attention: %d query heads for %d kv heads", Hq, Hkv);
+  if ((r1 == nullptr) != (r2 == nullptr)) return gb::fail(GB_BAD_ARGUMENT, "attention: the distance term takes both of its numbers");
+  if (chunk < 0 || (chunk > 0 && (window > 0 || keep_first > 0)))
+    return gb::fail(GB_BAD_ARGUMENT, "attention: a stretch of %d positions goes with no window", chunk);
   dim3 grid(T, (Hq + WARPS - 1) / WARPS);
   return GB_DISPATCH_DTYPE(dtype, TT, [&]() -> int {
     if (hd <= 256 && vd <= 256)
       attention_simple_kernel<TT, 256><<<grid, WARPS * 32, 0, stream>>>(
           (const TT*)q, (const TT*)k_pool, (const TT*)v_pool, block_table, table_width, cu_q, kv_lens,
-          token_req, (TT*)out, Hq, Hkv, hd, v_hd, vd, scale, window, page_size, softcap, keep_first, sink);
+          token_req, (TT*)out, Hq, Hkv, hd, v_hd, vd, scale, window, page_size, softcap, keep_first, sink, sink_v, r1, r2, chunk);
     else
       attention_simple_kernel<TT, WIDEST><<<grid, WARPS * 32, 0, stream>>>(
           (const TT*)q, (const TT*)k_pool, (const TT*)v_pool, block_table, table_width, cu_q, kv_lens,
-          token_req, (TT*)out, Hq, Hkv, hd, v_hd, vd, scale, window, page_size, softcap, keep_first, sink);
+          token_req, (TT*)out, Hq, Hkv, hd, v_hd, vd, scale, window, page_size, softcap, keep_first, sink, sink_v, r1, r2, chunk);
     return gb::check_launch("attention_simple");
   });
 }

@@ -14,7 +14,8 @@ constexpr int MAX_TOP = 32;
 // One block per token: its warps share out the experts (z_e = h . W[e] + b[e] in 32-bit, the bias
 // 32-bit, each logit one warp's sum in a fixed order), then warp 0 picks the `top` largest in
 // descending order (the lower index first among equals); weights = softmax over the chosen logits
-// (mode 0), or each chosen expert's own sigmoid(z_e), not renormalized (mode 1).
+// (mode 0), or each chosen expert's own sigmoid(z_e), not renormalized (mode 1), or its share of a
+// softmax over all E logits, not renormalized either (mode 2).
 template <typename HT, typename WT>
 __global__ void __launch_bounds__(256)
 route_topk_kernel(const HT* __restrict__ h, const WT* __restrict__ w, const float* __restrict__ bias, int T, int E,
@@ -38,6 +39,14 @@ route_topk_kernel(const HT* __restrict__ h, const WT* __restrict__ w, const floa
   }
   __syncthreads();
   if (warp != 0) return;
+  // the softmax over every expert needs the largest logit and the sum before logits are struck out
+  float all_max = -INFINITY, all_sum = 0.f;
+  if (mode == 2) {
+    for (int e = lane; e < E; e += 32) all_max = fmaxf(all_max, z[e]);
+    all_max = gb::warp_max(all_max);
+    for (int e = lane; e < E; e += 32) all_sum += expf(z[e] - all_max);
+    all_sum = gb::warp_sum(all_sum);
+  }
   // `top` rounds of a warp-wide arg-max; a chosen expert's logit is replaced by -inf
   float chosen[MAX_TOP];
   for (int j = 0; j < top; ++j) {
@@ -59,6 +68,8 @@ route_topk_kernel(const HT* __restrict__ h, const WT* __restrict__ w, const floa
   }
   if (lane == 0 && mode == 1) {
     for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] = 1.0f / (1.0f + expf(-chosen[j]));
+  } else if (lane == 0 && mode == 2) {
+    for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] = expf(chosen[j] - all_max) / all_sum;
   } else if (lane == 0) {
     const float largest = chosen[0];
     float sum = 0.f;
@@ -139,7 +150,7 @@ moe_down_kernel(const AT* __restrict__ act, const WT* __restrict__ w, const int3
 GB_EXPORT int gb_route_topk(const void* h, int h_dtype, const void* w, const float* bias, int w_dtype, int T, int E,
                             int K, int top, int mode, int32_t* ids, float* weights, cudaStream_t stream) {
   if (T <= 0) return GB_OK;
-  if (mode != 0 && mode != 1) return gb::fail(GB_BAD_ARGUMENT, "route_topk: mode %d", mode);
+  if (mode < 0 || mode > 2) return gb::fail(GB_BAD_ARGUMENT, "route_topk: mode %d", mode);
   if (E < 1 || E > MAX_EXPERTS || top < 1 || top > MAX_TOP || top > E)
     return gb::fail(GB_UNSUPPORTED, "route_topk: %d of %d experts (at most %d of %d)", top, E, MAX_TOP, MAX_EXPERTS);
   const size_t smem = (size_t)(E + K) * sizeof(float);

@@ -88,6 +88,7 @@ class CudaOps:
         self.core = load_kernel_lib("garuda_core")
         self._mixers = None
         self._state = None
+        self._seq = None
         self._declare_core()
         # A word of pinned host memory that a kernel whose bounded wait ran out writes its code to (the
         # device reaches pinned host memory directly); ``failed_wait`` reads it without a copy.
@@ -138,7 +139,7 @@ class CudaOps:
             "gb_gemm_simple": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
             "gb_attention_simple": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                                    c_int, c_float, c_int, c_int, c_void_p],
+                                    c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
             "gb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
             "gb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                           c_void_p],
@@ -181,6 +182,35 @@ class CudaOps:
                 fn.restype = c_int
             self._state = L
         return self._state
+
+    @property
+    def seq_lib(self):
+        """The library of the post-norm, gated-recurrence and convolved-projection kernels, compiled
+        and loaded when a model first needs it."""
+        if self._seq is None:
+            L = load_kernel_lib("garuda_seq")
+            L.gb_last_error.restype = ctypes.c_char_p
+            for name, argtypes in self._SEQ_SIGNATURES.items():
+                fn = getattr(L, name)
+                fn.argtypes = argtypes
+                fn.restype = c_int
+            L.gb_mingru_scratch_floats.argtypes = [c_int, c_int, c_int]
+            L.gb_mingru_scratch_floats.restype = c_longlong
+            self._seq = L
+        return self._seq
+
+    _SEQ_SIGNATURES = {
+        "gb_post_norm": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_void_p],
+        "gb_group_gate_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "gb_xielu": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+        "gb_mingru": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
+                      c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+        "gb_conv_qkv": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p,
+                        c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                        c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_float, c_int, c_void_p],
+        "gb_conv_state_shift": [c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
+                                c_void_p],
+    }
 
     _STATE_SIGNATURES = {
         "gb_streams_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
@@ -501,14 +531,21 @@ class CudaOps:
 
     def paged_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out,
                         scale, window, page_size, num_requests, max_q_len, max_kv_len, ws=None, min_q_len=1,
-                        value_dim=None, softcap: float = 0.0, keep_first: int = 0, sink: bool = False):
+                        value_dim=None, softcap: float = 0.0, keep_first: int = 0, sink: bool = False,
+                        sink_values=None, distance=None, chunk: int = 0):
         """``value_dim``: how many of a value row's first channels are the value (``out`` is then
         ``[T, Hq * value_dim]``); None: all ``hd``. A mixer whose keys and values are parts of one
         cached row passes the same pool for both and the narrower width; a value pool of its own may
         have rows of another width than the keys'. ``softcap`` c > 0: scores become ``c tanh(s / c)``.
         ``keep_first`` n: a windowed query also reads its request's first n positions. ``sink``: one
-        is added to the softmax's denominator (an entry of score zero without a value)."""
-        self._on_device(q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out)
+        is added to the softmax's denominator (an entry of score zero without a value).
+        ``sink_values`` (32-bit ``[Hq]``): ``exp(sink_values[h])`` is added there instead, a learned
+        number per head. ``distance = (r1, r2)`` (32-bit ``[Hq]`` each): ``r1[h] ln(1 + r2[h] (i - j))``
+        is taken off the score of key ``j`` for the query at ``i``. ``chunk`` n: a query reads only
+        the keys ``j <= i`` with ``floor(j / n) = floor(i / n)`` (no window then)."""
+        self._on_device(q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, sink_values)
+        r1, r2 = distance if distance is not None else (None, None)
+        self._on_device(r1, r2)
         T, Hq, hd = q.shape
         Hkv = k_pool.shape[1]
         v_hd = v_pool.shape[3]
@@ -519,8 +556,17 @@ class CudaOps:
               and k_pool.is_contiguous() and v_pool.is_contiguous(), "attention: pool shape")
         _need(0 < vd <= v_hd, "attention: value_dim must be within the row")
         _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attention: block table")
-        plain = softcap == 0.0 and keep_first == 0 and not sink and v_hd == hd
-        if not plain and self.tc is not None and q.dtype == torch.bfloat16 and vd == v_hd and self.tc.capped_attention(
+        for v in (sink_values, r1, r2):
+            _need(v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == Hq),
+                  "attention: one float32 number per query head")
+        _need(not chunk or not (window or keep_first), "attention: a chunked mask goes with no window")
+        extras = sink_values is not None or distance is not None or chunk > 0
+        plain = softcap == 0.0 and keep_first == 0 and not sink and v_hd == hd and not extras
+        if (extras and self.tc is not None and q.dtype == torch.bfloat16 and self.tc.extras_attention(
+                q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale, page_size, num_requests,
+                max_q_len, max_kv_len, ws, vd, softcap, sink_values, r1, r2, chunk, window, keep_first, sink, min_q_len)):
+            return
+        if not plain and not extras and self.tc is not None and q.dtype == torch.bfloat16 and vd == v_hd and self.tc.capped_attention(
                 q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale, window, page_size,
                 num_requests, max_q_len, max_kv_len, ws, softcap, keep_first, sink, min_q_len):
             return
@@ -537,7 +583,8 @@ class CudaOps:
             q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), _tag(q, "attention q"),
             block_table.data_ptr(), block_table.shape[1], cu_q.data_ptr(), kv_lens.data_ptr(),
             token_req.data_ptr(), out.data_ptr(), T, Hq, Hkv, hd, v_hd, vd, float(scale), int(window),
-            int(page_size), float(softcap), int(keep_first), int(bool(sink)), self._stream()), "attention")
+            int(page_size), float(softcap), int(keep_first), int(bool(sink)), _ptr(sink_values), _ptr(r1), _ptr(r2),
+            int(chunk), self._stream()), "attention")
 
     # ------------------------------------------------------------------ more norms and residual forms
     def layernorm(self, x, weight, bias, eps, out, rows=None):
@@ -627,12 +674,13 @@ class CudaOps:
         self.gated_act(tmp, act, kind, limit, group)
 
     # ------------------------------------------------------------------ routed experts
-    ROUTER_SCORES = {"softmax_chosen": 0, "sigmoid": 1}
+    ROUTER_SCORES = {"softmax_chosen": 0, "sigmoid": 1, "softmax_all": 2}
 
     def route_topk(self, h, w_router, bias, top, ids, weights, score: str = "softmax_chosen"):
         """Router logits ``h @ w_router^T + bias`` in 32-bit; ``ids[T, top]`` the experts with the
         largest logits (descending), ``weights[T, top]`` the softmax over those logits only, or
-        (``score`` "sigmoid") each chosen expert's ``sigmoid(logit)``, not renormalized."""
+        (``score`` "sigmoid") each chosen expert's ``sigmoid(logit)``, not renormalized, or
+        (``"softmax_all"``) its share of the softmax over all experts' logits, not renormalized."""
         self._on_device(h, w_router, bias, ids, weights)
         T, K = h.shape
         E = w_router.shape[0]
@@ -795,10 +843,11 @@ class CudaOps:
     def latent_rows(self, src, heads, dn, rot, rank, rotary, positions, q_nope, q_lat, norm_w, eps, token_req,
                     block_table, pool, page_size):
         """``latent_query_prepare`` and ``latent_append`` in one kernel, for a step's 32-bit rows
-        ``src [T, heads * (dn + rot) + rank + rot]``: queries first, then the latent and its key part."""
+        ``src [T, heads * (dn + rot) + rank + rot]`` (a view with any row stride): queries first, then
+        the latent and its key part."""
         self._on_device(src, positions, q_nope, q_lat, norm_w, token_req, block_table, pool)
         T = src.shape[0]
-        _need(src.dtype == torch.float32 and src.is_contiguous() and src.shape[1] == heads * (dn + rot) + rank + rot,
+        _need(src.dtype == torch.float32 and src.stride(1) == 1 and src.shape[1] == heads * (dn + rot) + rank + rot,
               "latent_rows: src")
         _need(q_nope.is_contiguous() and q_lat.is_contiguous() and q_nope.dtype == q_lat.dtype == pool.dtype
               and tuple(q_nope.shape) == (T, heads, dn) and tuple(q_lat.shape) == (T, heads, rank + rot), "latent_rows: outputs")
@@ -1118,6 +1167,131 @@ class CudaOps:
             y_ptrs, w_ptrs, n, 1.0 / n, float(eps if branch_eps is None else branch_eps), _ptr(gate),
             gate.stride(0) if gate is not None else 0, _ptr(gate_bias), _ptr(weight), float(eps), _ptr(x),
             None if x is not None else out.data_ptr(), _ptr(rounded), T, d, self._stream()), "sublayer_merge")
+
+    # ------------------------------------------------------------------ a norm after the sum; gates per head; xIELU
+    def post_norm(self, x, y, alpha, weight, eps, row=None, rounded=None):
+        """``x <- rms(alpha * x + y + row) * weight`` in place on the 32-bit residual ``x [T, d]``; ``y``
+        (32-bit ``[T, d]``) and ``row`` (32-bit ``[d]``) may be None. ``rounded`` (bfloat16 ``[T, d]``):
+        also the new ``x`` rounded, the input of the sublayer that reads it next. One pass."""
+        self._on_device(x, y, weight, row, rounded)
+        _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2, "post_norm: x must be float32 [T, d]")
+        T, d = x.shape
+        _need(y is None or (y.dtype == torch.float32 and y.is_contiguous() and tuple(y.shape) == (T, d)),
+              "post_norm: y must be float32 of x's shape")
+        _need(row is None or (row.dtype == torch.float32 and row.is_contiguous() and row.numel() == d), "post_norm: row float32 [d]")
+        _need(weight.numel() == d and weight.is_contiguous(), "post_norm: weight [d]")
+        _need(rounded is None or (rounded.dtype == torch.bfloat16 and rounded.is_contiguous() and tuple(rounded.shape) == (T, d)),
+              "post_norm: rounded bfloat16 [T, d]")
+        L = self.seq_lib
+        self._check(L, L.gb_post_norm(x.data_ptr(), _ptr(y), _ptr(row), float(alpha), weight.data_ptr(),
+                                      _tag(weight, "norm weight"), float(eps), _ptr(rounded), T, d, self._stream()), "post_norm")
+
+    def group_gate_mul(self, x, gate, group: int):
+        """``x[t, c] <- x[t, c] * sigmoid(gate[t, c // group])`` in place: one gate per head of
+        ``group`` channels; ``gate [T, n / group]`` 32-bit logits (a column range of a wider row will do)."""
+        self._on_device(x, gate)
+        T, n = x.shape
+        _need(x.is_contiguous() and gate.dtype == torch.float32 and gate.stride(1) == 1 and group >= 1 and n % group == 0
+              and tuple(gate.shape) == (T, n // group), "group_gate_mul: x contiguous [T, n], gate float32 [T, n / group]")
+        L = self.seq_lib
+        self._check(L, L.gb_group_gate_mul(x.data_ptr(), _tag(x, "group_gate_mul x"), gate.data_ptr(), gate.stride(0), T, n,
+                                           int(group), self._stream()), "group_gate_mul")
+
+    def xielu(self, z, out, a_pos: float, a_neg: float):
+        """``out = a_pos z^2 + z / 2`` where ``z > 0``, ``a_neg (exp(z) - 1 - z) + z / 2`` elsewhere;
+        32-bit arithmetic. Both may be column ranges of wider rows."""
+        self._on_device(z, out)
+        T, n = z.shape
+        _need(tuple(out.shape) == (T, n) and z.stride(1) == 1 and out.stride(1) == 1, "xielu: shapes")
+        L = self.seq_lib
+        self._check(L, L.gb_xielu(z.data_ptr(), _tag(z, "xielu in"), z.stride(0), out.data_ptr(), _tag(out, "xielu out"),
+                                  out.stride(0), T, n, float(a_pos), float(a_neg), self._stream()), "xielu")
+
+    def linear_xielu(self, ctx, a, w, out, a_pos: float, a_neg: float):
+        """``out[M,N] = xielu(a[M,K] @ w[N,K]^T)``, the activation in 32-bit on the 32-bit sums and
+        rounded once: in the product's epilogue where the tensor-core kernel takes the shape, else a
+        product into a 32-bit row and the activation kernel."""
+        self._on_device(a, w, out)
+        M, K = a.shape
+        N = w.shape[0]
+        _need(w.shape[1] == K and tuple(out.shape) == (M, N) and a.dtype == w.dtype, "linear_xielu: shapes and dtypes")
+        _need(a.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear_xielu: operands must be contiguous")
+        if self.tc is not None and a.dtype == torch.bfloat16 and self.tc.linear_xielu(a, w, out, a_pos, a_neg):
+            return
+        z = ctx.ws.get("linear_act_z", (M, N), torch.float32)
+        self.linear(a, w, z)
+        self.xielu(z, out, a_pos, a_neg)
+
+    # ------------------------------------------------------------------ a gated recurrence per channel
+    def mingru(self, ctx, proj, cols, bias_z, bias_u, state, out):
+        """The recurrent part of a minGRU mixer for one step. ``proj [T, P]`` (32-bit): the projected
+        row; ``cols = (z, u, g)`` the first columns of the gate's logits, the candidate's pre-activation
+        and the output gate's logits in it (``W`` wide each, ``W = out.shape[1]``). ``bias_z``,
+        ``bias_u``: 32-bit ``[W]`` or None. Per channel: ``z = sigmoid(.)``, candidate ``u + 1/2`` where
+        ``u >= 0`` and ``sigmoid(u)`` below, ``S <- (1 - z) S + z candidate``, ``out = S * silu(g)``.
+        ``state [slots, >= W]`` (32-bit): a request's ``S``; advanced for the batch's requests."""
+        b = ctx.batch
+        self._on_device(proj, bias_z, bias_u, state, out)
+        T, W = out.shape
+        cz, cu, cg = (int(c) for c in cols)
+        _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[0] == T
+              and max(cz, cu, cg) + W <= proj.shape[1], "mingru: a float32 row with three column ranges")
+        _need(all(v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == W) for v in (bias_z, bias_u)),
+              "mingru: float32 biases [W]")
+        _need(state.dtype == torch.float32 and state.stride(1) == 1 and state.shape[1] >= W, "mingru: state float32 [slots, W]")
+        _need(out.is_contiguous(), "mingru: out must be contiguous")
+        L = self.seq_lib
+        R = b.num_requests
+        need = int(L.gb_mingru_scratch_floats(R, W, int(b.max_q_len)))
+        scratch = ctx.ws.get("mingru_parts", (need,), torch.float32) if need else None
+        self._check(L, L.gb_mingru(proj.data_ptr(), proj.stride(0), cz, cu, cg, _ptr(bias_z), _ptr(bias_u), b.cu_q.data_ptr(),
+                                   b.slots.data_ptr(), state.data_ptr(), state.stride(0), out.data_ptr(), _tag(out, "mingru out"),
+                                   R, W, int(b.max_q_len), _ptr(scratch), self._stream()), "mingru", 2 if need else 1)
+
+    # ------------------------------------------------------------------ a short convolution in front of attention
+    def conv_qkv_append(self, ctx, proj, bias, conv_w, taps, state, q_out, k_pool, v_pool, block_table, heads, kv_heads,
+                        dim, vdim, q_weight, k_weight, eps, page_size, v_first_in=None, v_first_out=None, mix: float = 0.0):
+        """From a step's projected 32-bit rows ``proj [T, C]`` (``heads dim`` query, ``kv_heads dim`` key,
+        ``kv_heads vdim`` value columns; ``bias [C]`` 32-bit or None is added): a causal convolution
+        over time per channel (``conv_w [C, taps]`` 32-bit, the last column weighs the current token;
+        zeros before a request's first token), queries and keys divided by their root mean square per
+        head (``q_weight``, ``k_weight``: 32-bit ``[dim]``; None: no norm), values mixed with another
+        layer's (``v <- (1 - mix) v + mix v_first_in``, 32-bit ``[T, kv_heads vdim]``) or written out
+        for that (``v_first_out``); queries to ``q_out [T, heads, dim]``, keys and values into their
+        pages. ``state [slots, (taps - 1) C]`` (32-bit) holds every request's last ``taps - 1``
+        projected rows and is moved on."""
+        b = ctx.batch
+        self._on_device(proj, bias, conv_w, state, q_out, k_pool, v_pool, block_table, q_weight, k_weight, v_first_in, v_first_out)
+        T = proj.shape[0]
+        C = heads * dim + kv_heads * (dim + vdim)
+        _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] == C, "conv_qkv_append: proj float32 [T, C]")
+        _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == C), "conv_qkv_append: bias")
+        _need(conv_w.dtype == torch.float32 and conv_w.is_contiguous() and tuple(conv_w.shape) == (C, taps),
+              "conv_qkv_append: conv_w float32 [C, taps]")
+        _need(taps == 1 or (state is not None and state.dtype == torch.float32 and state.stride(1) == 1
+                            and state.shape[1] >= (taps - 1) * C), "conv_qkv_append: state float32 [slots, (taps - 1) C]")
+        _need(q_out.is_contiguous() and tuple(q_out.shape) == (T, heads, dim), "conv_qkv_append: q_out shape")
+        _need(k_pool.dtype == q_out.dtype == v_pool.dtype and k_pool.is_contiguous() and v_pool.is_contiguous()
+              and tuple(k_pool.shape[1:]) == (kv_heads, page_size, dim)
+              and tuple(v_pool.shape[1:]) == (kv_heads, page_size, vdim), "conv_qkv_append: pool shapes")
+        _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "conv_qkv_append: block table")
+        for v in (q_weight, k_weight):
+            _need(v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == dim), "conv_qkv_append: norm weights")
+        for v in (v_first_in, v_first_out):
+            _need(v is None or (v.dtype == torch.float32 and v.is_contiguous() and tuple(v.shape) == (T, kv_heads * vdim)),
+                  "conv_qkv_append: shared values float32 [T, kv_heads vdim]")
+        L = self.seq_lib
+        st_ptr, st_stride = (state.data_ptr(), state.stride(0)) if state is not None else (None, 0)
+        self._check(L, L.gb_conv_qkv(
+            proj.data_ptr(), proj.stride(0), _ptr(bias), conv_w.data_ptr(), GB_F32, int(taps), st_ptr, st_stride,
+            q_out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), _tag(q_out, "q_out"), b.positions.data_ptr(),
+            b.token_req.data_ptr(), b.cu_q.data_ptr(), b.slots.data_ptr(), block_table.data_ptr(), block_table.shape[1], T,
+            heads, kv_heads, dim, vdim, _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(v_first_in), _ptr(v_first_out),
+            float(mix), int(page_size), self._stream()), "conv_qkv")
+        if taps > 1:
+            self._check(L, L.gb_conv_state_shift(proj.data_ptr(), proj.stride(0), _ptr(bias), int(taps), C, st_ptr, st_stride,
+                                                 b.cu_q.data_ptr(), b.slots.data_ptr(), b.num_requests, self._stream()),
+                        "conv_state_shift")
 
     # ------------------------------------------------------------------ sampling
     def argmax(self, logits, out):

@@ -165,6 +165,11 @@ class TensorCoreKernels:
             return False
         return self._gemm(a, w, out, w.shape[0], 0, gate_act=self.STORE_ACTS[kind])
 
+    def linear_xielu(self, a, w, out, a_pos: float, a_neg: float) -> bool:
+        """``out = xielu(a w^T)`` in bfloat16, the activation on the 32-bit sums in the product's
+        epilogue; False where the product does not take the shape."""
+        return False
+
     def takes_qkv(self, h, w_qkv, q_out, head_dim) -> bool:
         """Whether the fused query/key/value product takes these operands (head sizes that
         divide 128, bfloat16, rows the TMA can address)."""
@@ -316,6 +321,13 @@ class TensorCoreKernels:
         self.ops._check(lib, code, "capped_attention",
                         ((2 if splits > 1 else 1) if has_decode else 0) + (1 if max_q_len * g > 16 else 0))
         return True
+
+    def extras_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale, page_size,
+                         num_requests, max_q_len, max_kv_len, ws, value_dim, softcap, sink_values, r1, r2, chunk,
+                         window, keep_first, sink, min_q_len=1) -> bool:
+        """Attention with a learned sink per head, a distance term on the scores or a chunked mask on
+        the tensor cores; False where no such kernel takes the shape."""
+        return False
 
     @staticmethod
     def capped_plan(num_requests: int, kv_heads: int, max_kv_len: int, window: int, keep_first: int) -> int:

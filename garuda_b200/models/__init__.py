@@ -1,2 +1,2 @@
 from .decoder import Decoder, ModelSpec, LayerCall, CacheGroup
-from . import llama, kavenex, murilorn, luvapel
+from . import llama, kavenex, murilorn, luvapel, midulorn

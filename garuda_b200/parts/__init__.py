@@ -7,12 +7,13 @@ from .base import (Part, Norm, PositionEncoding, Mixer, FeedForward, ResidualBra
                    SublayerGate)
 from .norm import RMSNorm, LayerNorm
 from .rotary import Rotary, NoPositions, RotaryParams
-from .attention import PagedAttention, CappedSinkAttention, NormedKeyAttention
+from .attention import PagedAttention, CappedSinkAttention, NormedKeyAttention, ConvolvedAttention
+from .mingru import MinGRU
 from .delta_rule import ChannelDeltaRule, HeadDeltaRule, GeneralDeltaRule
 from .mlp import SwiGLU, GatedFeedForward, PlainFeedForward
 from .latent_attention import LatentAttention
 from .experts import RoutedExperts
 from .token_side import TokenSide
-from .block import BlockSpec, PreNormBlock, SublayerNormBlock, LinearSigmoidGate, BranchOutputs
+from .block import BlockSpec, PreNormBlock, SublayerNormBlock, PostNormBlock, LinearSigmoidGate, BranchOutputs
 from .parallel import ParallelMixers
 from .hyper import StreamMixing, StreamPreNormBlock

@@ -19,7 +19,7 @@ from typing import Optional
 
 import torch
 
-from .base import (Mixer, PagedKV, TensorSpec, PartSpec, build_part, register_mixer)
+from .base import (FixedState, Mixer, PagedKV, TensorSpec, PartSpec, build_part, register_mixer)
 
 
 @register_mixer("paged_attention")
@@ -304,4 +304,147 @@ class NormedKeyAttention(Mixer):
             return None
         y = ws.get(out_name, (T, self.width), torch.float32)
         ops.linear(out, self.w_o, y)
+        return y
+
+
+@register_mixer("convolved_attention")
+class ConvolvedAttention(Mixer):
+    """Grouped-query attention over the paged cache behind a short causal convolution on every
+    projected channel, without a position encoding: positions enter through the mask and through a
+    term that grows with the distance. With ``x`` the mixer's input, query head ``n`` reading key/value
+    head ``n // (heads / kv_heads)``, each option off at its neutral value:
+
+        q, k, v = W_q x + b_q, W_k x + b_k, W_v x + b_v                       (``bias``)
+        y_t = sum_j w[c, j] u_(t - taps + 1 + j) per channel c of q, k, v    (``taps``; zeros before the start)
+        q, k <- rms(q) * w_q, rms(k) * w_k per head, the weights shared by the heads   (``qk_norm``)
+        v <- (1 - lambda) v + lambda v_first                                  (``value_mix="mix"``)
+        s_ij = (q_i . k_j) * scale - r1_n ln(1 + r2_n (i - j))                (``distance``)
+        i reads j  iff  j <= i and floor(i / chunk) = floor(j / chunk)        (``chunk``; None: every j <= i)
+        p_ij = exp(s_ij) / (exp(sink_n) + sum_j' exp(s_ij'))                  (``sink``)
+        out = W_o concat_n sum_j p_ij v_j + b_o
+
+    ``value_mix``: ``"source"`` marks the layer whose values (after the convolution) the later
+    layers mix into theirs; ``"mix"`` such a later layer, with ``lambda`` its tensor ``vmix``. Both name
+    the same ``value_mix_key``; the values travel in the step's context, for the step's tokens only.
+    The mixed values are what the cache holds. The convolution's state, the last ``taps - 1`` projected
+    rows of a request (biases included), is a ``FixedState`` beside the pages.
+    ``names``: the tensors' local names (a bias is the weight's name with ``.b`` added, a convolution's
+    taps ``.conv``, ``[channels, taps]`` with the last column on the current token)."""
+    graph_safe = True
+    scales_residual = True
+    defers_bias = True
+
+    def __init__(self, width: int, heads: int, kv_heads: int, dim: int, vdim: Optional[int] = None,
+                 scale: Optional[float] = None, taps: int = 0, qk_norm: bool = True, eps: float = 1e-6, bias: bool = True,
+                 distance: bool = False, chunk: Optional[int] = None, sink: bool = False, value_mix: Optional[str] = None,
+                 value_mix_key: str = "v_first", names: Optional[dict] = None, init_std: float = 0.02):
+        if heads % kv_heads:
+            raise ValueError(f"{heads} query heads are not a multiple of {kv_heads} kv heads")
+        if value_mix not in (None, "source", "mix"):
+            raise ValueError(f"value_mix is None, 'source' or 'mix', got {value_mix!r}")
+        self.width, self.heads, self.kv_heads, self.dim = int(width), int(heads), int(kv_heads), int(dim)
+        self.vdim = int(vdim) if vdim else self.dim
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.dim)
+        self.taps = max(int(taps or 0), 1)
+        self.qk_norm, self.eps, self.bias = bool(qk_norm), float(eps), bool(bias)
+        self.distance, self.sink = bool(distance), bool(sink)
+        self.chunk = int(chunk) if chunk else None
+        self.value_mix, self.value_mix_key = value_mix, value_mix_key
+        self.names = dict({"q": "q", "k": "k", "v": "v", "o": "o", "q_norm": "q.norm", "k_norm": "k.norm", "r1": "r1",
+                           "r2": "r2", "sink": "sink", "vmix": "vmix"}, **(names or {}))
+        self.init_std = float(init_std)
+        self.q_dim, self.k_dim, self.v_dim = self.heads * self.dim, self.kv_heads * self.dim, self.kv_heads * self.vdim
+        self.channels = self.q_dim + self.k_dim + self.v_dim
+
+    def tensors(self):
+        init, n = ("normal", self.init_std), self.names
+        t = {n["q"]: TensorSpec((self.q_dim, self.width), init=init), n["k"]: TensorSpec((self.k_dim, self.width), init=init),
+             n["v"]: TensorSpec((self.v_dim, self.width), init=init),
+             n["o"]: TensorSpec((self.width, self.heads * self.vdim), init=init)}
+        if self.bias:
+            for key, rows in (("q", self.q_dim), ("k", self.k_dim), ("v", self.v_dim), ("o", self.width)):
+                t[n[key] + ".b"] = TensorSpec((rows,), role="vector", init=("normal", 0.02))
+        if self.taps > 1:
+            for key, rows in (("q", self.q_dim), ("k", self.k_dim), ("v", self.v_dim)):
+                t[n[key] + ".conv"] = TensorSpec((rows, self.taps), role="vector", init=("normal", 0.5))
+        if self.qk_norm:
+            t[n["q_norm"]] = TensorSpec((self.dim,), role="vector", init=("normal_about_one", 0.1))
+            t[n["k_norm"]] = TensorSpec((self.dim,), role="vector", init=("normal_about_one", 0.1))
+        if self.distance:
+            t[n["r1"]] = TensorSpec((self.heads,), role="vector", init=("uniform", 0.1, 1.0))
+            t[n["r2"]] = TensorSpec((self.heads,), role="vector", init=("uniform", 0.05, 2.0))
+        if self.sink:
+            t[n["sink"]] = TensorSpec((self.heads,), role="vector", init=("normal", 1.0))
+        if self.value_mix is not None:
+            t[n["vmix"]] = TensorSpec((), role="vector", init=("uniform", 0.2, 0.8))
+        return t
+
+    def cache_need(self):
+        paged = PagedKV(self.kv_heads, self.dim, None, value_dim=self.vdim, chunk=self.chunk)
+        if self.taps > 1:
+            return (paged, FixedState(((self.taps - 1) * self.channels,)))
+        return paged
+
+    def load(self, tensors, ops, dtype):
+        super().load(tensors, ops, dtype)
+        n = self.names
+        keys = ("q", "k", "v")
+        self.w_qkv = torch.cat([tensors[n[k]] for k in keys], dim=0).contiguous()
+        self.b_qkv = torch.cat([tensors[n[k] + ".b"].float() for k in keys]).contiguous() if self.bias else None
+        self.conv_w = None
+        if self.taps > 1:
+            self.conv_w = torch.cat([tensors[n[k] + ".conv"].float() for k in keys], dim=0).contiguous()
+        else:
+            self.conv_w = torch.ones((self.channels, 1), dtype=torch.float32, device=self.w_qkv.device)
+        self.q_weight = tensors[n["q_norm"]].float().contiguous() if self.qk_norm else None
+        self.k_weight = tensors[n["k_norm"]].float().contiguous() if self.qk_norm else None
+        self.far = (tensors[n["r1"]].float().contiguous(), tensors[n["r2"]].float().contiguous()) if self.distance else None
+        self.sinks = tensors[n["sink"]].float().contiguous() if self.sink else None
+        self.mix = float(tensors[n["vmix"]].float().reshape(-1)[0]) if self.value_mix == "mix" else 0.0
+        self.w_o = tensors[n["o"]].contiguous()
+        self.output_bias = tensors[n["o"] + ".b"].float().contiguous() if self.bias else None
+        self._scaled_bias = {}
+
+    def _bias_times(self, alpha: float):
+        if alpha == 1.0:
+            return self.output_bias
+        if alpha not in self._scaled_bias:
+            self._scaled_bias[alpha] = (self.output_bias * alpha).contiguous()
+        return self._scaled_bias[alpha]
+
+    def forward(self, ctx, h, cache, residual=None, alpha: float = 1.0, defer_bias: bool = False):
+        b, ops, ws = ctx.batch, self.ops, ctx.ws
+        T = h.shape[0]
+        paged, state = (cache.parts[0], cache.parts[1].state) if cache.parts is not None else (cache, None)
+        if not cache.writes:
+            raise ValueError("a convolved attention keeps a cache of its own")
+        proj = ws.get("qkv", (T, self.channels), torch.float32)
+        ops.linear(h, self.w_qkv, proj)
+        q = ws.get("q_heads", (T, self.heads, self.dim), self.dtype)
+        v_in = v_out = None
+        key = ("shared_values", self.value_mix_key)
+        if self.value_mix == "source":
+            v_out = ws.get(f"shared_values_{self.value_mix_key}", (T, self.v_dim), torch.float32)
+            ctx.step_cache[key] = v_out
+        elif self.value_mix == "mix":
+            v_in = ctx.step_cache.get(key)
+            if v_in is None or tuple(v_in.shape) != (T, self.v_dim):
+                raise ValueError(f"no layer in front has left values '{self.value_mix_key}' of {self.v_dim} channels to mix in")
+        ops.conv_qkv_append(ctx, proj, self.b_qkv, self.conv_w, self.taps, state, q, paged.k, paged.v, paged.block_table,
+                            self.heads, self.kv_heads, self.dim, self.vdim, self.q_weight, self.k_weight, self.eps,
+                            paged.page_size, v_first_in=v_in, v_first_out=v_out, mix=self.mix)
+        out = ws.get("attn_ctx", (T, self.heads * self.vdim), self.dtype)
+        ops.paged_attention(q, paged.k, paged.v, paged.block_table, b.cu_q, b.kv_lens, b.token_req, out, self.scale, 0,
+                            paged.page_size, b.num_requests, b.max_q_len, b.max_kv_len, ws=ws, min_q_len=b.min_q_len,
+                            sink_values=self.sinks, distance=self.far, chunk=self.chunk or 0)
+        add_bias = self.output_bias is not None and not defer_bias
+        if residual is not None:
+            ops.linear(out, self.w_o, residual, accumulate=True, alpha=alpha)
+            if add_bias:
+                ops.residual_axpy(residual, None, 1.0, self._bias_times(alpha))
+            return None
+        y = ws.get("mixer_out", (T, self.width), torch.float32)
+        ops.linear(out, self.w_o, y)
+        if add_bias:
+            ops.residual_axpy(y, None, 1.0, self.output_bias)
         return y

@@ -30,7 +30,7 @@ class TensorSpec:
     contraction or an embedding table: held in the compute dtype), ``"vector"``
     (a norm weight or the like: a tensor stored in 32-bit stays 32-bit) or
     ``"table"`` (integers: held as int32). ``init`` describes the random-weights
-    mode: ``("normal", std)``, ``("ones",)``, ``("normal_about_one", std)`` or ``("normal_about_identity", std)``. A size that
+    mode: ``("normal", std)``, ``("ones",)``, ``("normal_about_one", std)``, ``("uniform", low, high)`` or ``("normal_about_identity", std)``. A size that
     the configuration does not give (the rank of a low-rank pair of matrices) is written ``None``
     in ``shape``: the loader takes what the file has there and checks the other sizes;
     random weights use ``free`` for it."""
@@ -53,12 +53,15 @@ class PagedKV:
     (garuda/src/cache/mod.rs:333-338); ``None`` keeps everything. ``value_dim``: the width of
     a value vector where it differs from the key's (``None``: ``head_dim``). ``keep_first``: with a
     window, the first positions of a request that every later query still reads; their pages stay
-    with the request while the pages between them and the window go back to the pool."""
+    with the request while the pages between them and the window go back to the pool. ``chunk``
+    n (instead of a window): a query reads only the positions of its own stretch of n,
+    ``floor(j / n) = floor(i / n)``; the pages of the stretches in front go back to the pool."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
     value_dim: Optional[int] = None
     keep_first: int = 0
+    chunk: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -118,6 +121,12 @@ class Part:
     #: output`` into the residual itself (a model's residual multiplier); for one that does not,
     #: the block scales and adds what it returns.
     scales_residual = False
+    #: A part whose output ends with a constant row (an output projection's bias) may say True and
+    #: keep that row, 32-bit ``[width]``, as ``output_bias``: a block that makes a pass over the residual
+    #: anyway then calls ``forward(..., defer_bias=True)``, gets the output without the row and adds
+    #: the row (scaled as the output is) in its own pass. Without ``defer_bias`` the part adds it itself.
+    defers_bias = False
+    output_bias = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
         return {}

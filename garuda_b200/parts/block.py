@@ -35,6 +35,8 @@ class BlockSpec:
     # for the arrangement that norms a sublayer's output: a gate on that output, per sublayer
     mixer_gate: Optional[PartSpec] = None
     feed_forward_gate: Optional[PartSpec] = None
+    # for the arrangement that norms after the sum: x <- norm(post_alpha * x + part(x))
+    post_alpha: float = 1.0
 
 
 @register_block("pre_norm")
@@ -277,3 +279,106 @@ class _RoundedInput:
 
 
 _ROUNDED_INPUT = _RoundedInput()
+
+
+@register_block("post_norm")
+class PostNormBlock:
+    """A layer whose norms come after the sums and whose sublayers read the residual itself:
+    ``x <- norm1(alpha * x + mixer(x)); x <- norm2(alpha * x + ffn(x))`` with ``alpha =
+    BlockSpec.post_alpha``. The residual is 32-bit; a sublayer's input is the residual rounded to the
+    compute dtype (the residual itself in 32-bit runs).
+
+    An RMS norm does not see a factor on its input but for ``eps``: ``rms_eps(alpha v) =
+    rms_(eps / alpha^2)(v)``. So a sublayer adds ``output / alpha`` into ``x`` (in its last product's
+    epilogue, like every other block's sublayers), and one pass over the row then norms ``x`` in
+    place with ``eps / alpha^2``, adds a deferred output bias on the way and writes the rounded
+    input of the sublayer that reads ``x`` next. A part that cannot add into the residual returns its
+    output, and the pass computes ``alpha * x + output`` as written."""
+
+    def __init__(self, spec: BlockSpec):
+        if spec.residual_mult != 1.0 or spec.branches or spec.mixer_connection is not None or spec.mixer_gate is not None:
+            raise ValueError("a layer that norms after the sum takes no multiplier, branches, streams or gates")
+        if not spec.post_alpha > 0:
+            raise ValueError(f"post_alpha must be positive, got {spec.post_alpha}")
+        self.spec = spec
+        self.alpha = float(spec.post_alpha)
+        self.mixer = build_part("mixer", spec.mixer)
+        self.mixer_norm = build_part("norm", spec.mixer_norm)
+        self.feed_forward = build_part("feed_forward", spec.feed_forward) if spec.feed_forward else None
+        self.feed_forward_norm = build_part("norm", spec.feed_forward_norm) if spec.feed_forward else None
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if norm is not None and not hasattr(norm, "fold"):
+                raise ValueError("a layer that norms after the sum takes RMS norms")
+
+    def parts(self):
+        s = self.spec
+        out = [(self.mixer_norm, s.mixer_norm.prefix), (self.mixer, s.mixer.prefix)]
+        if self.feed_forward is not None:
+            out += [(self.feed_forward_norm, s.feed_forward_norm.prefix), (self.feed_forward, s.feed_forward.prefix)]
+        return out
+
+    @property
+    def graph_safe(self):
+        return all(part.graph_safe for part, _ in self.parts())
+
+    def takes_pending_norm(self, ops):
+        """A layer in front that makes a pass over the row anyway writes this layer's rounded input."""
+        return _ROUNDED_INPUT
+
+    def _input(self, ctx, x, turn):
+        """The residual in the compute dtype. A 32-bit run gets a copy too: a part that adds into
+        the residual in its last product may read its input again after that (a shared expert behind
+        the routed ones)."""
+        h = ctx.ws.get(f"sublayer_in_{turn}", tuple(x.shape), ctx.dtype)
+        ctx.ops.cast(x, h)
+        return h
+
+    def _sublayer(self, ctx, x, h, part, norm, cache, turn):
+        """``x <- norm(alpha * x + part(h))``; ``turn``: also write the new ``x`` rounded into that
+        buffer and return it."""
+        weight, eps = norm.fold()
+        a = self.alpha
+        kw = {"defer_bias": True} if part.defers_bias else {}
+        args = (ctx, h) if cache is _NO_CACHE else (ctx, h, cache)
+        rounded = None
+        if turn is not None and ctx.dtype == torch.bfloat16:
+            rounded = ctx.ws.get(f"sublayer_in_{turn}", tuple(x.shape), ctx.dtype)
+        bias = part.output_bias if part.defers_bias else None
+        if part.scales_residual:
+            y = part.forward(*args, residual=x, alpha=1.0 / a, **kw)
+            if y is None:
+                if bias is not None:
+                    bias = self._scaled(part, bias, 1.0 / a)
+                ctx.ops.post_norm(x, None, 1.0, weight, eps / (a * a), row=bias, rounded=rounded)
+                return rounded
+        else:
+            y = part.forward(*args, **kw)
+            if y is None:
+                raise RuntimeError(f"{type(part).__name__} returned nothing although it was given no residual to add to")
+        ctx.ops.post_norm(x, y, a, weight, eps, row=bias, rounded=rounded)
+        return rounded
+
+    def _scaled(self, part, bias, factor):
+        cache = self.__dict__.setdefault("_bias_rows", {})
+        key = (id(part), factor)
+        if key not in cache:
+            cache[key] = (bias * factor).contiguous()
+        return cache[key]
+
+    def forward(self, ctx, x, cache, pending=None, next_norm=None):
+        """``pending``: this layer's input already rounded, by the layer in front. ``next_norm``: what
+        the next layer said it takes; if that is a rounded input, the last pass writes it and it is
+        returned."""
+        ctx.pending_norm = None
+        last = 1 if next_norm is _ROUNDED_INPUT else None
+        h = pending if pending is not None else self._input(ctx, x, 1)
+        ff = self.feed_forward
+        h2 = self._sublayer(ctx, x, h, self.mixer, self.mixer_norm, cache, 0 if ff is not None else last)
+        if ff is None:
+            return h2
+        if h2 is None:
+            h2 = self._input(ctx, x, 0)
+        return self._sublayer(ctx, x, h2, ff, self.feed_forward_norm, _NO_CACHE, last)
+
+
+_NO_CACHE = object()

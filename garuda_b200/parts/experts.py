@@ -9,6 +9,8 @@ weights, and an optional shared expert runs for every token.
 
 Variants, by constructor parameter: ``router_score="sigmoid"`` weighs a chosen expert by
 ``sigmoid(z_e)`` (the choice is still of the largest; nothing is renormalized);
+``router_score="softmax_all"`` weighs it by its share of the softmax over all experts' logits
+(not renormalized over the chosen either);
 ``scale_input=True`` puts the weight on what goes into the expert, ``out = sum_chosen
 expert_e(weight_e * h)``; ``router_bias=False`` drops ``b_r``; ``activation="silu"`` is the plain
 SiLU gate.
@@ -33,7 +35,7 @@ class RoutedExperts(FeedForward):
                  limit: float = 0.0, shared_inner: Optional[int] = None, shared_limit: float = 0.0,
                  router_bias: bool = True, init_std: float = 0.02, router_score: str = "softmax_chosen",
                  scale_input: bool = False):
-        if router_score not in ("softmax_chosen", "sigmoid"):
+        if router_score not in ("softmax_chosen", "sigmoid", "softmax_all"):
             raise ValueError(f"unknown router score {router_score!r}")
         self.router_score, self.scale_input = router_score, bool(scale_input)
         if not 1 <= top <= experts:

@@ -99,34 +99,53 @@ class GatedFeedForward(FeedForward):
 @register_feed_forward("plain")
 class PlainFeedForward(FeedForward):
     """``down(act(up h))`` without a gate: ``activation`` is ``"relu2"`` (the square of relu),
-    ``"silu"``, ``"tanh"`` or ``"sigmoid"``, computed in 32-bit on the product's 32-bit result and
-    rounded once. ``names``: the tensors' local names."""
-    graph_safe = True
+    ``"silu"``, ``"tanh"``, ``"sigmoid"`` or ``"xielu"``, computed in 32-bit on the product's 32-bit
+    result and rounded once. ``names``: the tensors' local names.
 
-    def __init__(self, width: int, inner: int, activation: str = "relu2", names=("up", "down"), init_std: float = 0.02):
-        if activation not in ("relu2", "silu", "tanh", "sigmoid"):
+    ``xielu`` has two learned numbers ``p, q`` (tensor ``act_name``, ``[2]``): ``softplus(p) z^2 + z / 2``
+    for ``z > 0`` and ``(1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2`` for ``z <= 0``; both factors are
+    formed once, in 64-bit, when the weights are loaded. The last product adds ``alpha * output`` into
+    the residual."""
+    graph_safe = True
+    scales_residual = True
+
+    def __init__(self, width: int, inner: int, activation: str = "relu2", names=("up", "down"), init_std: float = 0.02,
+                 act_name: str = "act"):
+        if activation not in ("relu2", "silu", "tanh", "sigmoid", "xielu"):
             raise ValueError(f"unknown activation {activation!r}")
         self.width, self.inner, self.activation = int(width), int(inner), activation
         self.names = tuple(names)
+        self.act_name = act_name
         self.init_std = float(init_std)
 
     def tensors(self):
         init = ("normal", self.init_std)
         u, d = self.names
-        return {u: TensorSpec((self.inner, self.width), init=init), d: TensorSpec((self.width, self.inner), init=init)}
+        t = {u: TensorSpec((self.inner, self.width), init=init), d: TensorSpec((self.width, self.inner), init=init)}
+        if self.activation == "xielu":
+            t[self.act_name] = TensorSpec((2,), role="vector", init=("normal", 0.5))
+        return t
 
     def load(self, tensors, ops, dtype):
         super().load(tensors, ops, dtype)
         u, d = self.names
         self.w_up = tensors[u].contiguous()
         self.w_down = tensors[d].contiguous()
+        if self.activation == "xielu":
+            import math
+            p, q = (float(v) for v in tensors[self.act_name].double().cpu())
+            softplus = lambda z: max(z, 0.0) + math.log1p(math.exp(-abs(z)))
+            self.a_pos, self.a_neg = softplus(p), 0.5 + softplus(q)
 
-    def forward(self, ctx, h, residual=None):
+    def forward(self, ctx, h, residual=None, alpha: float = 1.0):
         T = h.shape[0]
         act = ctx.ws.get("ffn_act", (T, self.inner), self.dtype)
-        self.ops.linear_act(ctx, h, self.w_up, act, self.activation)
+        if self.activation == "xielu":
+            self.ops.linear_xielu(ctx, h, self.w_up, act, self.a_pos, self.a_neg)
+        else:
+            self.ops.linear_act(ctx, h, self.w_up, act, self.activation)
         if residual is not None:
-            self.ops.linear(act, self.w_down, residual, accumulate=True)
+            self.ops.linear(act, self.w_down, residual, accumulate=True, alpha=alpha)
             return None
         y = ctx.ws.get("ffn_out", (T, self.width), torch.float32)
         self.ops.linear(act, self.w_down, y)

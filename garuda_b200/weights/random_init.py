@@ -33,6 +33,8 @@ def random_tensor(seed: int, name: str, shape, init) -> torch.Tensor:
         a = rng.standard_normal(shape, dtype=np.float32) * np.float32(init[1])
     elif kind == "normal_about_one":
         a = np.float32(1.0) + rng.standard_normal(shape, dtype=np.float32) * np.float32(init[1])
+    elif kind == "uniform":                    # between init[1] and init[2]
+        a = np.float32(init[1]) + rng.random(shape, dtype=np.float32) * np.float32(init[2] - init[1])
     elif kind == "normal_about_identity":      # a square matrix
         a = np.eye(shape[0], shape[1], dtype=np.float32) + rng.standard_normal(shape, dtype=np.float32) * np.float32(init[1])
     else:

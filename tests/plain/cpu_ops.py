@@ -127,9 +127,10 @@ class CpuOps:
     # garuda/src/llama/mod.rs:793-818; garuda/src/cache/mod.rs:333-338
     def paged_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out,
                         scale, window, page_size, num_requests, max_q_len, max_kv_len, ws=None, min_q_len=1,
-                        value_dim=None, softcap=0.0, keep_first=0, sink=False):
+                        value_dim=None, softcap=0.0, keep_first=0, sink=False, sink_values=None, distance=None, chunk=0):
         """softcap c: s <- c tanh(s / c); keep_first n: a windowed query also reads positions below n;
-        sink: p_j = exp(s_j) / (1 + sum exp(s_k))"""
+        sink: p_j = exp(s_j) / (1 + sum exp(s_k)); sink_values: exp(sink_values[h]) in place of the 1;
+        distance (r1, r2): s_j -= r1[h] ln(1 + r2[h] (pos - j)); chunk n: keys from floor(pos / n) n on"""
         T, Hq, hd = q.shape
         Hkv = k_pool.shape[1]
         g = Hq // Hkv
@@ -140,6 +141,8 @@ class CpuOps:
             q_len = int(cu_q[r + 1] - cu_q[r])
             pos = int(kv_lens[r]) - q_len + (t - int(cu_q[r]))
             start = max(0, pos + 1 - window) if window else 0
+            if chunk:
+                start = pos // chunk * chunk
             js = torch.arange(start, pos + 1)
             if window and keep_first and start > 0:
                 js = torch.cat([torch.arange(0, min(keep_first, start)), js])
@@ -151,7 +154,11 @@ class CpuOps:
                 s = (K[:, h // g, :] @ q[t, h].float()) * scale
                 if softcap:
                     s = softcap * torch.tanh(s / softcap)
-                if sink:
+                if distance is not None:
+                    s = s - float(distance[0][h]) * torch.log1p(float(distance[1][h]) * (pos - js).float())
+                if sink_values is not None:
+                    p = torch.softmax(torch.cat([s, sink_values[h].float().reshape(1)]), 0)[:-1]
+                elif sink:
                     p = torch.softmax(torch.cat([s, torch.zeros(1)]), 0)[:-1]
                 else:
                     p = torch.softmax(s, 0)
@@ -213,7 +220,10 @@ class CpuOps:
         order = torch.sort(-z, dim=-1, stable=True).indices[:, :top]
         ids.copy_(order.to(torch.int32))
         chosen = torch.gather(z, 1, order)
-        weights.copy_(torch.sigmoid(chosen) if score == "sigmoid" else torch.softmax(chosen, -1))
+        if score == "softmax_all":
+            weights.copy_(torch.gather(torch.softmax(z, -1), 1, order))
+        else:
+            weights.copy_(torch.sigmoid(chosen) if score == "sigmoid" else torch.softmax(chosen, -1))
 
     def moe_gate_up(self, h, w_gate_up, ids, act, kind, limit, in_scale=None):
         T, top = ids.shape
@@ -241,6 +251,80 @@ class CpuOps:
         act = torch.zeros(T, top, w_down.shape[2], dtype=h.dtype)
         self.moe_gate_up(h, w_gate_up, ids, act, kind, limit, weights if scale_input else None)
         self.moe_down(act, w_down, ids, None if scale_input else weights, x, alpha)
+
+    # ---- a norm after the sum, gates per head, xIELU, a gated recurrence per channel, convolved projections ----
+    def post_norm(self, x, y, alpha, weight, eps, row=None, rounded=None):
+        v = alpha * x
+        if y is not None:
+            v = v + y
+        if row is not None:
+            v = v + row
+        x.copy_(v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * weight.float())
+        if rounded is not None:
+            rounded.copy_(x.to(rounded.dtype))
+
+    def group_gate_mul(self, x, gate, group):
+        x.copy_((x.float() * torch.sigmoid(gate.float()).repeat_interleave(group, dim=1)).to(x.dtype))
+
+    def xielu(self, z, out, a_pos, a_neg):
+        z = z.float()
+        out.copy_(torch.where(z > 0, a_pos * z * z + 0.5 * z, a_neg * (torch.expm1(torch.clamp(z, max=0.0)) - z) + 0.5 * z).to(out.dtype))
+
+    def linear_xielu(self, ctx, a, w, out, a_pos, a_neg):
+        self.xielu(a.float() @ w.float().t(), out, a_pos, a_neg)
+
+    def mingru(self, ctx, proj, cols, bias_z, bias_u, state, out):
+        b = ctx.batch
+        W = out.shape[1]
+        cz, cu, cg = cols
+        for r in range(b.num_requests):
+            slot = int(b.slots[r])
+            S = state[slot, :W].clone() if slot >= 0 else torch.zeros(W)
+            for t in range(int(b.cu_q[r]), int(b.cu_q[r + 1])):
+                z = torch.sigmoid(proj[t, cz:cz + W] + (bias_z if bias_z is not None else 0.0))
+                u = proj[t, cu:cu + W] + (bias_u if bias_u is not None else 0.0)
+                n = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+                S = (1 - z) * S + z * n
+                g = proj[t, cg:cg + W]
+                out[t] = (S * g * torch.sigmoid(g)).to(out.dtype)
+            if slot >= 0:
+                state[slot, :W] = S
+
+    def conv_qkv_append(self, ctx, proj, bias, conv_w, taps, state, q_out, k_pool, v_pool, block_table, heads, kv_heads,
+                        dim, vdim, q_weight, k_weight, eps, page_size, v_first_in=None, v_first_out=None, mix=0.0):
+        b = ctx.batch
+        T, C = proj.shape
+        u = proj.float() + (bias.float() if bias is not None else 0.0)
+        y = torch.zeros(T, C)
+        keep = taps - 1
+        for r in range(b.num_requests):
+            t0, t1 = int(b.cu_q[r]), int(b.cu_q[r + 1])
+            slot = int(b.slots[r])
+            old = state[slot, :keep * C].reshape(keep, C).clone() if keep and slot >= 0 else torch.zeros(keep, C)
+            rows = torch.cat([old, u[t0:t1]], 0)          # the kept rows, then the step's
+            for j in range(taps):
+                y[t0:t1] += rows[j:j + t1 - t0] * conv_w[:, j].float()
+            if keep and slot >= 0:
+                state[slot, :keep * C] = rows[-keep:].reshape(-1)
+        nq, nk = heads * dim, kv_heads * dim
+
+        def rms(v, w):
+            return v if w is None else v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * w.float()
+
+        q_out.copy_(rms(y[:, :nq].reshape(T, heads, dim), q_weight).to(q_out.dtype))
+        k = rms(y[:, nq:nq + nk].reshape(T, kv_heads, dim), k_weight)
+        v = y[:, nq + nk:]
+        if v_first_out is not None:
+            v_first_out.copy_(v)
+        if v_first_in is not None:
+            v = (1.0 - mix) * v + mix * v_first_in
+        v = v.reshape(T, kv_heads, vdim)
+        for t in range(T):
+            pos = int(b.positions[t])
+            page = int(block_table[int(b.token_req[t]), pos // page_size])
+            if page >= 0:
+                k_pool[page, :, pos % page_size, :] = k[t].to(k_pool.dtype)
+                v_pool[page, :, pos % page_size, :] = v[t].to(v_pool.dtype)
 
     # ---- a residual of several streams ----
     def streams_rmsnorm(self, x, in_w, weight, eps, out, rows=None):
