@@ -37,7 +37,7 @@ class ChunkedAttentionConfig:
     dim: int
     vdim: int
     scale: float
-    taps: int                    # 1: no convolution
+    taps: Optional[int]          # None: no convolution
     chunk: Optional[int]         # mask.size: a query reads the positions of its own stretch of this many
     v_mix: bool
 
@@ -90,8 +90,8 @@ def _read_mixer(kind, m, wm):
     kv_heads = _get(m, "kv_heads", wm, int, 1)
     if heads % kv_heads:
         raise ConfigError(f"config.json: '{wm}heads' = {heads} is not a multiple of '{wm}kv_heads' = {kv_heads}")
-    taps = _get(m, "conv", wm, int, 1) if m.get("conv") is not None else 1
-    if taps > 16:
+    taps = _get(m, "conv", wm, int, 1) if m.get("conv") is not None else None
+    if taps is not None and taps > 16:
         raise ConfigError(f"config.json: '{wm}conv' = {taps}: at most 16 taps")
     chunk = _get(m["mask"], "size", wm + "mask.", int, 1) if m.get("mask") is not None else None
     return ChunkedAttentionConfig(heads, kv_heads, dim, vdim, scale, taps, chunk, bool(m.get("v_mix", False)))

@@ -2,11 +2,15 @@
 // 32-bit accumulation), flash-style, for the variants the plain kernels of attention_mma.cu do not
 // take: keys and values of widths of their own, scores capped by c tanh(s / c), a window that also
 // keeps a request's first positions, and a sink (one more entry of score zero, without a value, in
-// the softmax's denominator). No position encoding: positions enter through the mask only.
+// the softmax's denominator), or a learned sink per query head (exp(sink_h) there instead of one), a
+// term on the scores that grows with the logarithm of the distance, and a mask of fixed stretches
+// of positions in place of the window. No position encoding: positions enter through the mask and
+// the distance term only.
 //
-//   s_ij = (q_i . k_j) * scale;   cap c > 0:  s_ij <- c tanh(s_ij / c)
+//   s_ij = (q_i . k_j) * scale;   cap c > 0:  s_ij <- c tanh(s_ij / c);   s_ij -= r1_h ln(1 + r2_h (i - j))
 //   i reads j  iff  j <= i and (window == 0 or i - j < window or j < keep_first)
-//   p_ij = exp(s_ij - m_i) / (sink exp(-m_i) + sum_j' exp(s_ij' - m_i))
+//              or, chunk n > 0:  j <= i and floor(j / n) = floor(i / n)
+//   p_ij = exp(s_ij - m_i) / (sink exp(-m_i) + sum_j' exp(s_ij' - m_i)),  sink = 1 or exp(sink_h)
 //
 // Scores, the cap, the running maximum and sum are 32-bit; probabilities are rounded to bfloat16
 // only as an operand of the second product. The rows of a query tile are (token, head-of-group)
@@ -56,7 +60,24 @@ struct Params {
   float* partials;               // [R, Hkv, splits, ROWS_DECODE, PR] (DECODE with splits > 1)
   int table_width, Hq, Hkv, g, window, keep_first, page_size, sink, splits;
   float scale, softcap;
+  const float* sink_v;           // [Hq] or null: a learned sink per query head
+  const float* r1;               // [Hq] or null: the distance term's two numbers per query head
+  const float* r2;
+  int chunk;                     // > 0: a query reads its own stretch of this many positions (no window then)
 };
+
+// First position that the query at `pos` reads (kept first positions aside).
+__device__ __forceinline__ int first_seen(const Params& p, int pos) {
+  if (p.chunk > 0) return pos / p.chunk * p.chunk;
+  return p.window > 0 ? max(0, pos + 1 - p.window) : 0;
+}
+
+// What the sink adds to a row's denominator, in units of exp(-m).
+__device__ __forceinline__ float sink_term(const Params& p, int head, float m) {
+  if (m == -INFINITY) return 0.f;
+  if (p.sink_v != nullptr) return fast_exp2((p.sink_v[head] - m) * 1.4426950408889634f);
+  return p.sink ? fast_exp2(-m * 1.4426950408889634f) : 0.f;
+}
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -127,10 +148,12 @@ struct State {
 
 // KEYS keys (from column key_off of the tile) for one warp's 16 rows. MASKED false: every key of the
 // tile is seen by every row (no comparison per score).
-template <int KEYS, bool MASKED>
+// FAR: the distance term, far1 ln(1 + far2 (i - j)) with the row's head's numbers, is taken off.
+template <int KEYS, bool MASKED, bool FAR>
 __device__ __forceinline__ void process(State& st, const uint32_t (&qf)[HD / 16][4], const __nv_bfloat16* ks,
                                         const __nv_bfloat16* vs, int key_off, int key0, const int (&row_pos)[2],
-                                        const int (&row_start)[2], const Params& p) {
+                                        const int (&row_start)[2], const float (&far1)[2], const float (&far2)[2],
+                                        const Params& p) {
   const int lane = threadIdx.x & 31;
   float s[KEYS / 8][4];
 #pragma unroll
@@ -186,8 +209,14 @@ __device__ __forceinline__ void process(State& st, const uint32_t (&qf)[HD / 16]
     for (int e = 0; e < 4; ++e) {
       const int i = e >> 1;
       float v = s[n][e];
+      const int j = key0 + key_off + n * 8 + (lane % 4) * 2 + (e & 1);
+      if (FAR) {
+        // ln(1 + x) = log2(1 + x) ln 2; a key behind the row (masked below) is given distance zero
+        const float dist = (float)max(row_pos[i] - j, 0);
+        v -= far1[i] * __log2f(fmaf(far2[i], dist, 1.0f));
+        s[n][e] = v;
+      }
       if (MASKED) {
-        const int j = key0 + key_off + n * 8 + (lane % 4) * 2 + (e & 1);
         const bool seen = j <= row_pos[i] && (j >= row_start[i] || j < p.keep_first);
         v = seen ? v : -INFINITY;
         s[n][e] = v;
@@ -240,7 +269,7 @@ __device__ __forceinline__ void process(State& st, const uint32_t (&qf)[HD / 16]
 }
 
 // grid (x, Hkv, R): TILE: x a tile of 64 rows of the request; DECODE: x one of p.splits shares of the keys.
-template <bool DECODE>
+template <bool DECODE, bool FAR>
 __global__ void __launch_bounds__(THREADS, (HD <= 64 && VD <= 64) ? 4 : 2)
 capped_attention_kernel(const Params p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -262,8 +291,9 @@ capped_attention_kernel(const Params p) {
   const int ntok = min(tokens_per_tile, q_len - tok0);
   const int nrows = ntok * p.g;
   const int pos0 = kv_len - q_len + tok0;
-  const int lo = p.window > 0 ? max(0, pos0 + 1 - p.window) : 0;
+  const int lo = first_seen(p, pos0);
   const int hi = pos0 + ntok - 1;
+  const int last_start = first_seen(p, hi);          // the first position that the tile's last row reads
   const int tile_begin = lo / KT, tile_end = hi / KT + 1;
   // tiles below the window that hold kept first positions
   const int kept_tiles = (p.window > 0 && p.keep_first > 0) ? min((p.keep_first + KT - 1) / KT, tile_begin) : 0;
@@ -298,7 +328,17 @@ capped_attention_kernel(const Params p) {
   for (int i = 0; i < 2; ++i) {
     const int row = my_rows + lane / 4 + 8 * i;
     row_pos[i] = row < nrows ? pos0 + row / p.g : -1;
-    row_start[i] = (row < nrows && p.window > 0) ? max(0, row_pos[i] + 1 - p.window) : 0;
+    row_start[i] = row < nrows ? first_seen(p, row_pos[i]) : 0;
+  }
+  float far1[2] = {0.f, 0.f}, far2[2] = {0.f, 0.f};
+  if (FAR) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int row = my_rows + lane / 4 + 8 * i;
+      const int head = kvh * p.g + (row < nrows ? row % p.g : 0);
+      far1[i] = p.r1[head] * 0.6931471805599453f;
+      far2[i] = p.r2[head];
+    }
   }
   State st;
 #pragma unroll
@@ -325,13 +365,13 @@ capped_attention_kernel(const Params p) {
     if (works) {
       // no mask where the tile lies wholly before the first row's position and inside the last row's window
       const int t0 = tile_of(w) * KT;
-      const bool full = w >= kept_tiles && t0 + KT - 1 <= pos0 && (p.window <= 0 || t0 >= hi + 1 - p.window);
+      const bool full = w >= kept_tiles && t0 + KT - 1 <= pos0 && t0 >= last_start;
       if (DECODE) {
-        if (full) process<16, false>(st, qf, ks, vs, warp * 16, t0, row_pos, row_start, p);
-        else process<16, true>(st, qf, ks, vs, warp * 16, t0, row_pos, row_start, p);
+        if (full) process<16, false, FAR>(st, qf, ks, vs, warp * 16, t0, row_pos, row_start, far1, far2, p);
+        else process<16, true, FAR>(st, qf, ks, vs, warp * 16, t0, row_pos, row_start, far1, far2, p);
       } else {
-        if (full) process<KT, false>(st, qf, ks, vs, 0, t0, row_pos, row_start, p);
-        else process<KT, true>(st, qf, ks, vs, 0, t0, row_pos, row_start, p);
+        if (full) process<KT, false, FAR>(st, qf, ks, vs, 0, t0, row_pos, row_start, far1, far2, p);
+        else process<KT, true, FAR>(st, qf, ks, vs, 0, t0, row_pos, row_start, far1, far2, p);
       }
     }
     __syncthreads();
@@ -347,8 +387,7 @@ capped_attention_kernel(const Params p) {
     for (int i = 0; i < 2; ++i) {
       const int row = my_rows + lane / 4 + 8 * i;
       if (row >= nrows) continue;
-      float l = st.l[i];
-      if (p.sink && st.m[i] != -INFINITY) l += fast_exp2(-st.m[i] * LOG2E);
+      const float l = st.l[i] + sink_term(p, kvh * p.g + row % p.g, st.m[i]);
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       __nv_bfloat16* dst = p.out + ((size_t)(q_begin + tok0 + row / p.g) * p.Hq + kvh * p.g + row % p.g) * VD;
 #pragma unroll
@@ -395,7 +434,7 @@ capped_attention_kernel(const Params p) {
         dst[VD + 1] = l;
       }
     } else {
-      if (p.sink && m != -INFINITY) l += fast_exp2(-m * LOG2E);
+      l += sink_term(p, kvh * p.g + row % p.g, m);
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       p.out[((size_t)(q_begin + row / p.g) * p.Hq + kvh * p.g + row % p.g) * VD + c] = __float2bfloat16_rn(o * inv);
     }
@@ -423,7 +462,7 @@ capped_attention_merge_kernel(const Params p) {
       o = fmaf(pr[c], f, o);
       l = fmaf(pr[VD + 1], f, l);
     }
-    if (p.sink && m != -INFINITY) l += fast_exp2(-m * LOG2E);
+    l += sink_term(p, kvh * p.g + row % p.g, m);
     const float inv = l > 0.f ? 1.0f / l : 0.f;
     p.out[((size_t)(q_begin + row / p.g) * p.Hq + kvh * p.g + row % p.g) * VD + c] = __float2bfloat16_rn(o * inv);
   }
@@ -447,9 +486,12 @@ GB_EXPORT int gb_capped_attention(const void* q, const void* k_pool, const void*
                                   const int32_t* block_table, int table_width, const int32_t* cu_q,
                                   const int32_t* kv_lens, int T, int R, int Hq, int Hkv, float scale, float softcap,
                                   int window, int keep_first, int sink, int page_size, int max_q_len, int min_q_len,
-                                  int splits, void* scratch, long long scratch_bytes, cudaStream_t stream) {
+                                  int splits, void* scratch, long long scratch_bytes, const float* sink_v, const float* r1,
+                                  const float* r2, int chunk, cudaStream_t stream) {
   if (T <= 0 || R <= 0) return GB_OK;
   if (Hkv < 1 || Hq % Hkv) return gb::fail(GB_BAD_ARGUMENT, "capped_attention: %d query heads for %d kv heads", Hq, Hkv);
+  if ((r1 == nullptr) != (r2 == nullptr)) return gb::fail(GB_BAD_ARGUMENT, "capped_attention: the distance term takes both of its numbers");
+  if (chunk < 0 || (chunk > 0 && window > 0)) return gb::fail(GB_BAD_ARGUMENT, "capped_attention: a stretch of %d positions goes with no window", chunk);
   const int g = Hq / Hkv;
   if (g > ROWS_TILE) return gb::fail(GB_UNSUPPORTED, "capped_attention: a group of %d query heads per kv head", g);
   splits = splits < 1 ? 1 : (splits > MAX_SPLITS ? MAX_SPLITS : splits);
@@ -462,16 +504,23 @@ GB_EXPORT int gb_capped_attention(const void* q, const void* k_pool, const void*
   p.table_width = table_width; p.Hq = Hq; p.Hkv = Hkv; p.g = g; p.window = window;
   p.keep_first = window > 0 ? keep_first : 0; p.page_size = page_size; p.sink = sink; p.splits = splits;
   p.scale = scale; p.softcap = softcap;
+  p.sink_v = sink_v; p.r1 = r1; p.r2 = r2; p.chunk = chunk;
+  const bool far = r1 != nullptr;
+  auto decode_kernel = far ? capped_attention_kernel<true, true> : capped_attention_kernel<true, false>;
+  auto tile_kernel = far ? capped_attention_kernel<false, true> : capped_attention_kernel<false, false>;
   static gb::OncePerDevice configured;
   if (configured.needed()) {
-    cudaError_t e1 = cudaFuncSetAttribute(capped_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
-    cudaError_t e2 = cudaFuncSetAttribute(capped_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
-    if (e1 != cudaSuccess || e2 != cudaSuccess)
-      return gb::fail(GB_CUDA_ERROR, "capped_attention: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+    cudaError_t e = cudaSuccess;
+    for (auto k : {capped_attention_kernel<false, false>, capped_attention_kernel<true, false>,
+                   capped_attention_kernel<false, true>, capped_attention_kernel<true, true>}) {
+      const cudaError_t e1 = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+      if (e1 != cudaSuccess) e = e1;
+    }
+    if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "capped_attention: %s", cudaGetErrorString(e));
     configured.done();
   }
   if (min_q_len * g <= ROWS_DECODE) {
-    int rc = gb::check_pdl_launch(gb::launch_pdl(capped_attention_kernel<true>, dim3(splits, Hkv, R), dim3(THREADS), SMEM,
+    int rc = gb::check_pdl_launch(gb::launch_pdl(decode_kernel, dim3(splits, Hkv, R), dim3(THREADS), SMEM,
                                                  stream, dim3(1, 1, 1), p), "capped_attention (decode)");
     if (rc) return rc;
     if (splits > 1) {
@@ -483,7 +532,7 @@ GB_EXPORT int gb_capped_attention(const void* q, const void* k_pool, const void*
   if (max_q_len * g > ROWS_DECODE) {
     const int tokens_per_tile = ROWS_TILE / g;
     dim3 grid((max_q_len + tokens_per_tile - 1) / tokens_per_tile, Hkv, R);
-    return gb::check_pdl_launch(gb::launch_pdl(capped_attention_kernel<false>, grid, dim3(THREADS), SMEM, stream,
+    return gb::check_pdl_launch(gb::launch_pdl(tile_kernel, grid, dim3(THREADS), SMEM, stream,
                                                dim3(1, 1, 1), p), "capped_attention (tile)");
   }
   return GB_OK;

@@ -106,11 +106,14 @@ struct EpilogueArgs {
   // GATE_CLAMPED_SWISH g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit)
   int gate_act = 0;
   float gate_limit = 0.f;
+  // STORE_XIELU: the factor on exp(z) - 1 - z for z <= 0 (gate_limit holds the factor on z^2 for z > 0)
+  float act_second = 0.f;
 };
 
 enum GateAct : int { GATE_SILU = 0, GATE_GELU_TANH = 1, GATE_CLAMPED_SWISH = 2,
                      // of one value, in the storing epilogue (EPI_STORE | EPI_GENERAL, bfloat16 out): relu(z)^2, tanh(z)
-                     STORE_RELU2 = 3, STORE_TANH = 4 };
+                     // xIELU: a z^2 + z / 2 for z > 0, b (exp(z) - 1 - z) + z / 2 for z <= 0, a = gate_limit, b = act_second
+                     STORE_RELU2 = 3, STORE_TANH = 4, STORE_XIELU = 5 };
 
 // This CTA's slice of `bytes` at `base` into L2 (cta of ctas; 16-byte granules), by one thread.
 __device__ __forceinline__ void prefetch_slice_l2(const uint8_t* base, long long bytes, int cta, int ctas) {
@@ -231,6 +234,10 @@ __device__ __forceinline__ float store_act_fast(const EpilogueArgs& ra, float z)
   if (ra.gate_act == STORE_RELU2) {
     const float r = fmaxf(z, 0.f);
     return r * r;
+  }
+  if (ra.gate_act == STORE_XIELU) {
+    const float half = 0.5f * z;
+    return z > 0.f ? fmaf(ra.gate_limit * z, z, half) : fmaf(ra.act_second, __expf(z) - 1.0f - z, half);
   }
   return 1.0f - 2.0f * __frcp_rn(__expf(2.0f * z) + 1.0f);
 }
@@ -1621,9 +1628,11 @@ GB_EXPORT int gb_gemm_tc_supported(const void* x, const void* w, int Mx, int Nw,
 // 2: w holds gate and up rows packed in groups of 64 ([128 * ceil(Nw / 64), K], see the head of this
 // file); out[Mx,Nw] (bf16) = act(x gate^T, x up^T), act by gate_act: silu(g) u unless told otherwise.
 // alpha: the accumulating epilogue adds alpha * product. gate_act, gate_limit: the gated epilogue's
-// activation (GateAct), or with epi 0 and a bfloat16 output STORE_RELU2 / STORE_TANH: out = act(x w^T).
+// activation (GateAct), or with epi 0 and a bfloat16 output STORE_RELU2 / STORE_TANH / STORE_XIELU: out =
+// act(x w^T); act_second: the second number of an activation that has two (STORE_XIELU).
 GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw, int K, int out_dtype, int epi,
-                         const GbNormFold* norm, float alpha, int gate_act, float gate_limit, cudaStream_t stream) {
+                         const GbNormFold* norm, float alpha, int gate_act, float gate_limit, float act_second,
+                         cudaStream_t stream) {
   if (!gb_gemm_tc_supported(x, w, Mx, Nw, K))
     return gb::fail(GB_UNSUPPORTED, "gemm_tc: needs K a multiple of 8 and 16-byte aligned operands (K = %d)", K);
   if ((epi & 7) == EPI_ACCUMULATE && out_dtype != GB_F32)
@@ -1634,13 +1643,14 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, void* out, int Mx, int Nw
   EpilogueArgs ra{};
   fold_norm(ra, norm);
   take_next_stream(ra);
-  if (gate_act < GATE_SILU || gate_act > STORE_TANH) return gb::fail(GB_BAD_ARGUMENT, "gemm_tc: activation %d", gate_act);
+  if (gate_act < GATE_SILU || gate_act > STORE_XIELU) return gb::fail(GB_BAD_ARGUMENT, "gemm_tc: activation %d", gate_act);
   if (gate_act >= STORE_RELU2 && ((epi & 7) != EPI_STORE || out_dtype != GB_BF16))
     return gb::fail(GB_BAD_ARGUMENT, "gemm_tc: an activation of one value goes with the storing epilogue and a bfloat16 output");
   if (gate_act < STORE_RELU2 && (epi & 7) != EPI_SWIGLU) gate_act = GATE_SILU;       // means nothing to the other epilogues
   ra.alpha = alpha;
   ra.gate_act = gate_act;
   ra.gate_limit = gate_limit;
+  ra.act_second = act_second;
   if (ra.h_out != nullptr && (epi & 7) != EPI_ACCUMULATE)
     return gb::fail(GB_UNSUPPORTED, "gemm_tc: a norm is folded in behind accumulating products only (epilogue %d)", epi);
   CUtensorMap mm, mn;

@@ -61,7 +61,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 latent_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool,
                         __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                         const int32_t* __restrict__ block_table, int table_width, const int32_t* __restrict__ cu_q,
-                        const int32_t* __restrict__ kv_lens, int H, float sc, int page_size, int splits) {
+                        const int32_t* __restrict__ kv_lens, int H, float sc, int page_size, int splits,
+                        const float* __restrict__ sink_v) {
   extern __shared__ __align__(16) unsigned char smem[];
   unsigned char* q_s = smem;
   unsigned char* k_s = smem + BM * PITCH;
@@ -238,6 +239,11 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   }
   const size_t gr0 = grow0 + rb * 16 + g, gr1 = gr0 + 8;
   if (splits == 1) {
+    // a learned sink per head: exp(sink_h) in the denominator, without a key or a value (m is in powers of two)
+    if (sink_v != nullptr) {
+      if (i0 < rows && m0 != -INFINITY) l0 += fast_exp2(sink_v[i0 % H] * 1.4426950408889634f - m0);
+      if (i1 < rows && m1 != -INFINITY) l1 += fast_exp2(sink_v[i1 % H] * 1.4426950408889634f - m1);
+    }
     const float inv0 = l0 > 0.f ? 1.0f / l0 : 0.f, inv1 = l1 > 0.f ? 1.0f / l1 : 0.f;
 #pragma unroll
     for (int n = 0; n < VCOLS / 8; ++n) {
@@ -262,7 +268,7 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 // One block per query row: the splits' sums brought to a common maximum and added in split order.
 __global__ void __launch_bounds__(128)
 latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
-                    int splits) {
+                    int splits, const float* __restrict__ sink_v, int H) {
   const size_t row = blockIdx.x;
   const float* ml = part_ml + row * splits * 2;
   float mx = -INFINITY;
@@ -270,6 +276,7 @@ latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ 
   float den = 0.f;
   for (int s = 0; s < splits; ++s)
     if (ml[2 * s] != -INFINITY) den += ml[2 * s + 1] * fast_exp2(ml[2 * s] - mx);
+  if (sink_v != nullptr && mx != -INFINITY) den += fast_exp2(sink_v[row % H] * 1.4426950408889634f - mx);
   const float inv = den > 0.f ? 1.0f / den : 0.f;
   for (int c = threadIdx.x; c < RANK; c += blockDim.x) {
     float num = 0.f;
@@ -293,10 +300,11 @@ GB_EXPORT long long gb_latent_attention_scratch_bytes(long long rows, int splits
 
 // q [T, H, ROW], pool [pages, 1, page_size, ROW], out [T, H * RANK], all bfloat16. max_q_len: the most
 // tokens a request brings (the grid's extent). splits: CTAs that share a tile's keys (1: none).
+// sink_v ([H] 32-bit, or null): exp(sink_v[h]) joins head h's softmax denominator.
 GB_EXPORT int gb_latent_attention(const void* q, const void* pool, void* out, const int32_t* block_table,
                                   int table_width, const int32_t* cu_q, const int32_t* kv_lens, int T,
                                   int num_requests, int H, float scale, int page_size, int max_q_len, int splits,
-                                  void* scratch, long long scratch_bytes, cudaStream_t stream) {
+                                  void* scratch, long long scratch_bytes, const float* sink_v, cudaStream_t stream) {
   if (T <= 0 || num_requests <= 0) return GB_OK;
   if (H < 1 || page_size < 1 || max_q_len < 1 || splits < 1 || !(scale > 0.f))
     return gb::fail(GB_BAD_ARGUMENT, "latent_attention: heads %d, page size %d, scale %g", H, page_size, (double)scale);
@@ -315,9 +323,9 @@ GB_EXPORT int gb_latent_attention(const void* q, const void* pool, void* out, co
   dim3 grid(tiles, num_requests, splits);
   latent_attention_kernel<<<grid, THREADS, SMEM, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, (__nv_bfloat16*)out, part_o, part_ml, block_table,
-      table_width, cu_q, kv_lens, H, scale * 1.4426950408889634f, page_size, splits);
+      table_width, cu_q, kv_lens, H, scale * 1.4426950408889634f, page_size, splits, sink_v);
   int rc = gb::check_launch("latent_attention");
   if (rc != GB_OK || splits == 1) return rc;
-  latent_merge_kernel<<<(unsigned)rows, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, splits);
+  latent_merge_kernel<<<(unsigned)rows, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, splits, sink_v, H);
   return gb::check_launch("latent_merge");
 }

@@ -31,7 +31,7 @@ class TensorCoreKernels:
         L = self.lib
         L.gb_last_error.restype = ctypes.c_char_p
         L.gb_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                 ctypes.POINTER(NormFold), c_float, c_int, c_float, c_void_p]
+                                 ctypes.POINTER(NormFold), c_float, c_int, c_float, c_float, c_void_p]
         L.gb_gemm_tc.restype = c_int
         L.gb_gemm_tc_grouped.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
                                          c_float, c_int, c_float, c_void_p]
@@ -121,7 +121,7 @@ class TensorCoreKernels:
                 self._plan = None          # another step than the one that was recorded
 
     def _gemm(self, x, w, out, n_out, epi, fold=None, alpha: float = 1.0, gate_act: int = 0,
-              gate_limit: float = 0.0) -> bool:
+              gate_limit: float = 0.0, act_second: float = 0.0) -> bool:
         M, K = x.shape
         if not self.lib.gb_gemm_tc_supported(x.data_ptr(), w.data_ptr(), M, n_out, K):
             return False
@@ -129,7 +129,7 @@ class TensorCoreKernels:
         tag = 0 if out.dtype == torch.float32 else 1
         code = self.lib.gb_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, n_out, K, tag, epi,
                                    None if fold is None else ctypes.byref(fold), float(alpha), int(gate_act),
-                                   float(gate_limit), self.ops._stream())
+                                   float(gate_limit), float(act_second), self.ops._stream())
         self.ops._check(self.lib, code, "gemm_tc")
         return True
 
@@ -168,7 +168,9 @@ class TensorCoreKernels:
     def linear_xielu(self, a, w, out, a_pos: float, a_neg: float) -> bool:
         """``out = xielu(a w^T)`` in bfloat16, the activation on the 32-bit sums in the product's
         epilogue; False where the product does not take the shape."""
-        return False
+        if w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+            return False
+        return self._gemm(a, w, out, w.shape[0], 0, gate_act=5, gate_limit=a_pos, act_second=a_neg)
 
     def takes_qkv(self, h, w_qkv, q_out, head_dim) -> bool:
         """Whether the fused query/key/value product takes these operands (head sizes that
@@ -288,10 +290,12 @@ class TensorCoreKernels:
         return True
 
     def capped_attention(self, q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale, window,
-                         page_size, num_requests, max_q_len, max_kv_len, ws, softcap, keep_first, sink, min_q_len=1) -> bool:
-        """Attention with capped scores, kept first positions, a sink or values of another width
-        than the keys on the tensor cores; False where no such kernel takes the shape (widths that
-        are no multiple of 16 or beyond 128, groups of more than 64 heads)."""
+                         page_size, num_requests, max_q_len, max_kv_len, ws, softcap, keep_first, sink, min_q_len=1,
+                         sink_values=None, r1=None, r2=None, chunk: int = 0) -> bool:
+        """Attention with capped scores, kept first positions, a sink (one, or a learned number per
+        head), a distance term, a chunked mask or values of another width than the keys on the tensor
+        cores; False where no such kernel takes the shape (widths that are no multiple of 16 or beyond
+        128, groups of more than 64 heads)."""
         T, Hq, hd = q.shape
         Hkv, vd = k_pool.shape[1], v_pool.shape[3]
         if hd % 16 or vd % 16 or hd > 128 or vd > 128 or Hq // Hkv > 64:
@@ -301,14 +305,14 @@ class TensorCoreKernels:
             lib = load_kernel_lib(capped_attention_lib_name(hd, vd))
             lib.gb_last_error.restype = ctypes.c_char_p
             lib.gb_capped_attention.argtypes = ([c_void_p] * 5 + [c_int] + [c_void_p] * 2 + [c_int] * 4 + [c_float, c_float]
-                                                + [c_int] * 7 + [c_void_p, ctypes.c_longlong, c_void_p])
+                                                + [c_int] * 7 + [c_void_p, ctypes.c_longlong] + [c_void_p] * 3 + [c_int, c_void_p])
             lib.gb_capped_attention.restype = c_int
             lib.gb_capped_attention_scratch_bytes.argtypes = [c_int, c_int, c_int]
             lib.gb_capped_attention_scratch_bytes.restype = ctypes.c_longlong
             self._capped[(hd, vd)] = lib
         g = Hq // Hkv
         has_decode = min_q_len * g <= 16
-        splits = self.capped_plan(num_requests, Hkv, max_kv_len, window, keep_first) if has_decode else 1
+        splits = self.capped_plan(num_requests, Hkv, max_kv_len, window or chunk, keep_first) if has_decode else 1
         need = int(lib.gb_capped_attention_scratch_bytes(num_requests, Hkv, splits))
         scratch = None
         if need:
@@ -317,7 +321,9 @@ class TensorCoreKernels:
             q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), block_table.data_ptr(),
             block_table.shape[1], cu_q.data_ptr(), kv_lens.data_ptr(), T, num_requests, Hq, Hkv, float(scale),
             float(softcap), int(window), int(keep_first), int(bool(sink)), int(page_size), int(max_q_len), int(min_q_len),
-            int(splits), None if scratch is None else scratch.data_ptr(), need, self.ops._stream())
+            int(splits), None if scratch is None else scratch.data_ptr(), need,
+            None if sink_values is None else sink_values.data_ptr(), None if r1 is None else r1.data_ptr(),
+            None if r2 is None else r2.data_ptr(), int(chunk), self.ops._stream())
         self.ops._check(lib, code, "capped_attention",
                         ((2 if splits > 1 else 1) if has_decode else 0) + (1 if max_q_len * g > 16 else 0))
         return True
@@ -326,8 +332,20 @@ class TensorCoreKernels:
                          num_requests, max_q_len, max_kv_len, ws, value_dim, softcap, sink_values, r1, r2, chunk,
                          window, keep_first, sink, min_q_len=1) -> bool:
         """Attention with a learned sink per head, a distance term on the scores or a chunked mask on
-        the tensor cores; False where no such kernel takes the shape."""
-        return False
+        the tensor cores; False where no such kernel takes the shape. Keys and values that are parts of
+        one cached row that every head reads go to the latent kernel (which knows the sink), everything
+        else to the kernel of the capped attention."""
+        T, Hq, hd = q.shape
+        if k_pool.data_ptr() == v_pool.data_ptr() and k_pool.shape[1] == 1 and value_dim < hd:
+            if r1 is not None or chunk or window or softcap or sink or keep_first:
+                return False
+            return self.latent_attention(q, k_pool, out, block_table, cu_q, kv_lens, value_dim, scale, page_size, num_requests,
+                                         max_q_len, max_kv_len, ws, sink_values=sink_values)
+        if value_dim != v_pool.shape[3]:
+            return False
+        return self.capped_attention(q, k_pool, v_pool, block_table, cu_q, kv_lens, token_req, out, scale, window, page_size,
+                                     num_requests, max_q_len, max_kv_len, ws, softcap, keep_first, sink, min_q_len,
+                                     sink_values=sink_values, r1=r1, r2=r2, chunk=chunk)
 
     @staticmethod
     def capped_plan(num_requests: int, kv_heads: int, max_kv_len: int, window: int, keep_first: int) -> int:
@@ -353,7 +371,7 @@ class TensorCoreKernels:
             lib = load_kernel_lib(latent_attention_lib_name(rank, rot))
             lib.gb_last_error.restype = ctypes.c_char_p
             lib.gb_latent_attention.argtypes = ([c_void_p] * 4 + [c_int] + [c_void_p] * 2 + [c_int] * 3 + [c_float]
-                                                + [c_int] * 3 + [c_void_p, ctypes.c_longlong, c_void_p])
+                                                + [c_int] * 3 + [c_void_p, ctypes.c_longlong, c_void_p, c_void_p])
             lib.gb_latent_attention.restype = c_int
             lib.gb_latent_attention_scratch_bytes.argtypes = [ctypes.c_longlong, c_int]
             lib.gb_latent_attention_scratch_bytes.restype = ctypes.c_longlong
@@ -371,8 +389,9 @@ class TensorCoreKernels:
         return max(1, min(296 // tiles, -(-max_kv_len // 128), 16))
 
     def latent_attention(self, q, pool, out, block_table, cu_q, kv_lens, rank, scale, page_size, num_requests,
-                         max_q_len, max_kv_len, ws=None) -> bool:
-        """``q [T, H, rank + rot]``, ``pool [pages, 1, page_size, rank + rot]``, ``out [T, H * rank]``."""
+                         max_q_len, max_kv_len, ws=None, sink_values=None) -> bool:
+        """``q [T, H, rank + rot]``, ``pool [pages, 1, page_size, rank + rot]``, ``out [T, H * rank]``.
+        ``sink_values`` (32-bit ``[H]``): a learned sink per head in the softmax's denominator."""
         T, H, row = q.shape
         rot = row - rank
         if q.dtype != torch.bfloat16 or not self.takes_latent(rank, rot) or not scale > 0:
@@ -388,6 +407,7 @@ class TensorCoreKernels:
         code = lib.gb_latent_attention(
             q.data_ptr(), pool.data_ptr(), out.data_ptr(), block_table.data_ptr(), block_table.shape[1],
             cu_q.data_ptr(), kv_lens.data_ptr(), T, num_requests, H, float(scale), int(page_size), int(max_q_len),
-            int(splits), None if scratch is None else scratch.data_ptr(), need, self.ops._stream())
+            int(splits), None if scratch is None else scratch.data_ptr(), need,
+            None if sink_values is None else sink_values.data_ptr(), self.ops._stream())
         self.ops._check(lib, code, "latent_attention", 1 if splits == 1 else 2)
         return True

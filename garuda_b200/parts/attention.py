@@ -345,6 +345,7 @@ class ConvolvedAttention(Mixer):
         self.width, self.heads, self.kv_heads, self.dim = int(width), int(heads), int(kv_heads), int(dim)
         self.vdim = int(vdim) if vdim else self.dim
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.dim)
+        self.has_conv = bool(taps)               # (one tap is a convolution too: a factor per channel)
         self.taps = max(int(taps or 0), 1)
         self.qk_norm, self.eps, self.bias = bool(qk_norm), float(eps), bool(bias)
         self.distance, self.sink = bool(distance), bool(sink)
@@ -364,7 +365,7 @@ class ConvolvedAttention(Mixer):
         if self.bias:
             for key, rows in (("q", self.q_dim), ("k", self.k_dim), ("v", self.v_dim), ("o", self.width)):
                 t[n[key] + ".b"] = TensorSpec((rows,), role="vector", init=("normal", 0.02))
-        if self.taps > 1:
+        if self.has_conv:
             for key, rows in (("q", self.q_dim), ("k", self.k_dim), ("v", self.v_dim)):
                 t[n[key] + ".conv"] = TensorSpec((rows, self.taps), role="vector", init=("normal", 0.5))
         if self.qk_norm:
@@ -392,7 +393,7 @@ class ConvolvedAttention(Mixer):
         self.w_qkv = torch.cat([tensors[n[k]] for k in keys], dim=0).contiguous()
         self.b_qkv = torch.cat([tensors[n[k] + ".b"].float() for k in keys]).contiguous() if self.bias else None
         self.conv_w = None
-        if self.taps > 1:
+        if self.has_conv:
             self.conv_w = torch.cat([tensors[n[k] + ".conv"].float() for k in keys], dim=0).contiguous()
         else:
             self.conv_w = torch.ones((self.channels, 1), dtype=torch.float32, device=self.w_qkv.device)

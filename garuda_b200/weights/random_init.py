@@ -39,7 +39,8 @@ def random_tensor(seed: int, name: str, shape, init) -> torch.Tensor:
         a = np.eye(shape[0], shape[1], dtype=np.float32) + rng.standard_normal(shape, dtype=np.float32) * np.float32(init[1])
     else:
         raise ValueError(f"unknown initialiser {init!r}")
-    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32))
+    # (ascontiguousarray alone would turn a number without dimensions into one of shape [1])
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).reshape(tuple(shape))
 
 
 def random_weights(config_dict: dict, seed: int, norm_init=None, store_dtype=torch.float32,
