@@ -278,7 +278,7 @@ def test_router_over_all_experts(both, T, E, K, top):
     same = (ids_g.cpu() == ids)
     assert same.float().mean() > 0.98                                # (two experts within rounding of each other may swap)
     close(wts_g.cpu()[same], wts[same], torch.float32, "router weights", 1e-4)
-    assert (wts_g.sum(-1) <= 1.0 + 1e-5).all() and (top == E or (wts_g.sum(-1) < 1.0).all())
+    assert (wts_g.sum(-1) <= 1.0 + 1e-5).all()                       # shares of the whole softmax: not renormalized
 
 
 # ---------------------------------------------------------------------------- the engine, replayed
