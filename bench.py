@@ -7,6 +7,7 @@
 
     python bench.py --design murilorn [--size 2k,4k]    (likewise for the third architecture)
     python bench.py --design luvapel [--size 2k,4k]     (the fourth, beside the third)
+    python bench.py --design midulorn [--size 2k,4k]    (the fifth, beside the third)
     python bench.py --design kavenex [--size 2k,4k]     (a JSON line of its own: the second architecture
                                                          beside Llama at equal sizes, kernel beside like kernel)
 
@@ -1105,6 +1106,259 @@ def run_design_luvapel(args) -> dict:
     return out
 
 
+# ``--design midulorn``: the Midulorn design beside the Murilorn decoder (the closest of the engine's models:
+# attention with a sink and biases and no position encoding, a recurrence behind short convolutions, routed
+# experts) at equal width, heads, head sizes and depth (random weights). Four layers: chunked attention behind
+# convolutions with a dense feed-forward, latent attention with experts, a gated recurrence with a dense
+# feed-forward, chunked attention with experts.
+MIDULORN_SIZES = {
+    "2k": dict(width=2048, heads=32, kv_heads=4, dim=64, chunk=1024, taps=4, l_heads=16, l_dim=64, rot_dim=32, l_vdim=64,
+               kv_rank=256, gru=4096, ff=5632, experts=16, top=4, expert_ff=1408, vocab=32000,
+               d_heads=16, d_kv_heads=16, d_dim=128, d_vdim=128, rank=64),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, chunk=1024, taps=4, l_heads=32, l_dim=64, rot_dim=32, l_vdim=64,
+               kv_rank=512, gru=8192, ff=11008, experts=16, top=4, expert_ff=2752, vocab=32000,
+               d_heads=32, d_kv_heads=16, d_dim=128, d_vdim=128, rank=128),
+}
+
+
+def midulorn_configs(z):
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["expert_ff"]}}
+    att = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                                          "scale": z["dim"] ** -0.5, "conv": z["taps"], "mask": {"size": z["chunk"]}, "v_mix": True}}
+    lat = {"type": "latent_attention", "mixer": {"heads": z["l_heads"], "dim": z["l_dim"], "rot_dim": z["rot_dim"], "vdim": z["l_vdim"],
+                                                 "kv_rank": z["kv_rank"], "scale": (z["l_dim"] + z["rot_dim"]) ** -0.5,
+                                                 "rot": {"base": 10000.0, "dims": z["rot_dim"]}}}
+    gru = {"type": "mingru", "mixer": {"width": z["gru"]}}
+    midulorn = {"architecture": "Midulorn", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0},
+                "norm": {"eps": 1e-5}, "postln_alpha": 2.0, "logit_scale": 1.0, "max_positions": 4096,
+                "layers": [dict(att, mlp=dense), dict(lat, mlp=moe), dict(gru, mlp=dense), dict(att, mlp=moe)]}
+    attn = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                                           "scale": z["dim"] ** -0.5, "softcap": 30.0, "mask": {"size": z["chunk"], "keep_first": 4}}}
+    delta = {"type": "channel_delta", "mixer": {"heads": z["d_heads"], "kv_heads": z["d_kv_heads"], "dim": z["d_dim"],
+                                                "vdim": z["d_vdim"], "conv": z["taps"], "decay_rank": z["rank"], "gate_rank": z["rank"]}}
+    murilorn = {"architecture": "Murilorn", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0},
+                "norm": {"eps": 1e-5}, "streams": 2, "logit_scale": 1.0, "logit_softcap": 30.0, "max_positions": 4096,
+                "layers": [dict(m, mlp=moe) for m in (attn, delta, delta, attn)]}
+    return midulorn, murilorn
+
+
+def run_design_midulorn(args) -> dict:
+    """Prefill and decode throughput of the Midulorn design and of the Murilorn decoder at equal sizes, and
+    the design's kernels beside the like kernels of the engine's other models, each against its roofline (the
+    slower of bytes / measured copy rate and FLOPs / measured bfloat16 rate)."""
+    import numpy as np
+    import torch
+    from garuda_b200 import Engine, StepEntry
+    from garuda_b200.engine.batch import Workspace
+    from garuda_b200.weights import write_random_model
+
+    hbm_peak, tflops_peak, peak_kind = peaks()
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    dev = torch.device("cuda:0")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(reps):
+            flush.zero_()
+            s, e = ev(), ev()
+            torch.cuda.synchronize()
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e))
+        return sorted(times)[len(times) // 2]
+
+    def roof(ms, flops=0.0, nbytes=0.0):
+        ideal = max(flops / (tflops_peak * 1e12), nbytes / (hbm_peak * 1e9)) * 1e3
+        return {"ms": round(ms, 4), "roofline_ms": round(ideal, 4), "frac": round(ideal / ms, 4)}
+
+    out = {"design": "midulorn", "beside": "murilorn", "peaks": peak_kind, "hbm_gbs": hbm_peak, "bf16_tflops": tflops_peak,
+           "dtype": "bf16", "data": "synthetic",
+           "timing": "CUDA events, 3 warm-up runs, L2 flushed before every timed run, median", "sizes": {}}
+    B, CTX, T = 8, 2048, PREFILL_TOKENS
+    for name in (args.size.split(",") if args.size else list(MIDULORN_SIZES)):
+        z = MIDULORN_SIZES[name]
+        rec, engines = {}, {}
+        for arch, cfg in zip(("midulorn", "murilorn"), midulorn_configs(z)):
+            tmp = tempfile.mkdtemp(prefix="garuda_bench_", dir="/dev/shm" if os.path.isdir("/dev/shm") else None)
+            try:
+                write_random_model(tmp, cfg, seed=0, store_dtype=torch.bfloat16)
+                engine = Engine(tmp, dtype="bfloat16", context=4096, page_size=32, kv_tokens=B * CTX + 4096 + 64,
+                                max_concurrent=B, max_batch_tokens=T, prefill_chunk=T, ignore_eos=True)
+            finally:
+                shutil.rmtree(tmp, ignore_errors=True)
+            engines[arch] = engine
+            runner, rng, V = engine.runner, np.random.default_rng(0), z["vocab"]
+            toks = rng.integers(0, V, T).tolist()
+            rid = [0]
+
+            def prefill():
+                rid[0] += 1
+                runner.run([StepEntry(10_000 + rid[0], toks, [T - 1])])
+                runner.end(10_000 + rid[0])
+
+            ms = timed(prefill, reps=5)
+            rec[arch] = {"prefill_2048_ms": round(ms, 3), "prefill_tok_s": round(T / ms * 1e3)}
+            steps = 48
+            for r in range(B):
+                runner.run([StepEntry(r, rng.integers(0, V, CTX - steps - 8).tolist(), [])])
+            feed = rng.integers(0, V, (steps + 8, B))
+            for i in range(8):
+                runner.run([StepEntry(r, [int(feed[i, r])], [0]) for r in range(B)])
+            marks = [ev() for _ in range(steps + 1)]
+            torch.cuda.synchronize()
+            marks[0].record()
+            for i in range(steps):
+                runner.run([StepEntry(r, [int(feed[8 + i, r])], [0]) for r in range(B)])
+                marks[i + 1].record()
+            torch.cuda.synchronize()
+            each = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
+            for r in range(B):
+                runner.end(r)
+            rec[arch].update({"decode_b8_ctx2048_ms": round(each[len(each) // 2], 4),
+                              "decode_tok_s": round(B / each[len(each) // 2] * 1e3),
+                              "graph_replays": runner.graphs.replays,
+                              "kernels_per_decode_step": runner.graphs.launches_replayed(B)})
+            if engine.ops.tc is not None:
+                engine.ops.tc.check_errors()
+        # ------------------------------------------------------------ kernel beside like kernel
+        ops = engines["midulorn"].ops
+        bf = torch.bfloat16
+        H, Hkv, hd, W, ps, chunk = z["heads"], z["kv_heads"], z["dim"], z["width"], 32, z["chunk"]
+        ws = Workspace(dev)
+
+        class Ctx:
+            pass
+
+        class Bt:
+            pass
+        ctx = Ctx()
+        ctx.ws = ws
+        ctx.step_cache = {}
+        kern = {}
+        for label, nreq, q_len, kv_len in (("prefill_2048", 1, T, T), ("decode_b8_ctx2048", B, 1, CTX)):
+            pages = (kv_len + ps - 1) // ps
+            n = nreq * q_len
+            bt = torch.arange(nreq * pages, dtype=torch.int32, device=dev).view(nreq, pages)
+            cu = torch.arange(nreq + 1, dtype=torch.int32, device=dev) * q_len
+            kvl = torch.full((nreq,), kv_len, dtype=torch.int32, device=dev)
+            req = torch.arange(nreq, dtype=torch.int32, device=dev).repeat_interleave(q_len)
+            pos = (torch.arange(q_len, dtype=torch.int32, device=dev) + (kv_len - q_len)).repeat(nreq)
+            b = Bt()
+            b.cu_q, b.token_req, b.positions, b.kv_lens = cu, req, pos, kvl
+            b.slots = torch.arange(nreq, dtype=torch.int32, device=dev)
+            b.num_requests, b.max_q_len, b.min_q_len = nreq, q_len, q_len
+            ctx.batch = b
+            # chunked attention with sinks and the distance term, beside Murilorn's windowed one of as many keys
+            q = torch.randn(n, H, hd, device=dev).to(bf)
+            kp, vp = (torch.randn(nreq * pages, Hkv, ps, hd, device=dev).to(bf) for _ in range(2))
+            o = torch.empty(n, H * hd, dtype=bf, device=dev)
+            sinks, r1, r2 = torch.randn(H, device=dev), torch.rand(H, device=dev), torch.rand(H, device=dev)
+            seen = [p % chunk + 1 for p in range(kv_len - q_len, kv_len)]
+            tiles = -(-max(seen) // 64) * 64 if q_len == 1 else sum(-(-min(c, kv_len) // 64) * 64 for c in (chunk,) * (kv_len // chunk))
+            cost = (4.0 * H * hd * nreq * sum(seen), 2.0 * (2 * nreq * min(kv_len, max(seen) if q_len == 1 else kv_len) * Hkv * hd + q.numel() + o.numel()))
+            ms = timed(lambda: ops.paged_attention(q, kp, vp, bt, cu, kvl, req, o, hd ** -0.5, 0, ps, nreq, q_len, kv_len, ws=ws,
+                                                   min_q_len=q_len, sink_values=sinks, distance=(r1, r2), chunk=chunk))
+            kern[f"chunked_attention_{label}"] = roof(ms, *cost)
+            win = max(seen) if q_len == 1 else chunk
+            keys = nreq * sum(min(p + 1, win) for p in range(kv_len - q_len, kv_len))
+            cost_w = (4.0 * H * hd * keys, 2.0 * (2 * nreq * min(kv_len, win + q_len) * Hkv * hd + q.numel() + o.numel()))
+            ms = timed(lambda: ops.paged_attention(q, kp, vp, bt, cu, kvl, req, o, hd ** -0.5, win, ps, nreq, q_len, kv_len, ws=ws,
+                                                   min_q_len=q_len, softcap=30.0, keep_first=4, sink=True))
+            kern[f"murilorn_capped_sink_attention_{label}"] = roof(ms, *cost_w)
+            # latent attention with sinks, beside the same kernel without (Kavenex's)
+            LH, rank, rot = z["l_heads"], z["kv_rank"], z["rot_dim"]
+            ql = torch.randn(n, LH, rank + rot, device=dev).to(bf)
+            pool = torch.randn(nreq * pages, 1, ps, rank + rot, device=dev).to(bf)
+            ol = torch.empty(n, LH * rank, dtype=bf, device=dev)
+            lsinks = torch.randn(LH, device=dev)
+            causal = nreq * sum(p + 1 for p in range(kv_len - q_len, kv_len))
+            cost_l = (2.0 * LH * (2 * rank + rot) * causal, 2.0 * (nreq * kv_len * (rank + rot) + ql.numel() + ol.numel()))
+            ms = timed(lambda: ops.paged_attention(ql, pool, pool, bt, cu, kvl, req, ol, 0.1, 0, ps, nreq, q_len, kv_len, ws=ws,
+                                                   min_q_len=q_len, value_dim=rank, sink_values=lsinks))
+            kern[f"latent_attention_with_sinks_{label}"] = roof(ms, *cost_l)
+            ms = timed(lambda: ops.paged_attention(ql, pool, pool, bt, cu, kvl, req, ol, 0.1, 0, ps, nreq, q_len, kv_len, ws=ws,
+                                                   min_q_len=q_len, value_dim=rank))
+            kern[f"kavenex_latent_attention_{label}"] = roof(ms, *cost_l)
+            # the projected row into queries and pages: convolved and normed here, biased there
+            C = (H + 2 * Hkv) * hd
+            row, bias = torch.randn(n, C, device=dev), torch.zeros(C, device=dev)
+            cw, qw, kw = torch.randn(C, z["taps"], device=dev), torch.ones(hd, device=dev), torch.ones(hd, device=dev)
+            cstate = torch.zeros(nreq, (z["taps"] - 1) * C, device=dev)
+            vf = torch.randn(n, Hkv * hd, device=dev)
+            moved = 4.0 * row.numel() + 2.0 * row.numel() + 4.0 * vf.numel() + 2 * 4.0 * cstate.numel()
+            ms = timed(lambda: ops.conv_qkv_append(ctx, row, bias, cw, z["taps"], cstate, q, kp, vp, bt, H, Hkv, hd, hd, qw, kw, 1e-5, ps,
+                                                   v_first_in=vf, mix=0.5))
+            kern[f"convolve_norm_mix_store_{label}"] = roof(ms, 0, moved)
+            ms = timed(lambda: ops.qkv_bias_append(row, bias, q, kp, vp, pos, req, bt, H, Hkv, hd, hd, ps))
+            kern[f"murilorn_bias_store_{label}"] = roof(ms, 0, 4.0 * row.numel() + 2.0 * row.numel())
+            # the recurrences: bytes are their rows in and out and the state
+            G = z["gru"]
+            proj = torch.randn(n, 3 * G, device=dev)
+            bz, bu = torch.randn(G, device=dev), torch.randn(G, device=dev)
+            gstate = torch.zeros(nreq, G, device=dev)
+            go = torch.empty(n, G, dtype=bf, device=dev)
+            ms = timed(lambda: ops.mingru(ctx, proj, (0, G, 2 * G), bz, bu, gstate, go))
+            kern[f"gated_recurrence_{label}"] = roof(ms, 0, 4.0 * proj.numel() + 2.0 * go.numel() + 2 * 4.0 * gstate.numel())
+            dH, dG, dd, dv, taps = z["d_heads"], z["d_kv_heads"], z["d_dim"], z["d_vdim"], z["taps"]
+            DC = 2 * dG * dd + dH * dv
+            conv_w, a_log, nw = torch.randn(DC, taps, device=dev) * 0.3, torch.randn(dH, device=dev) * 0.3, torch.ones(dv, device=dev)
+            dstate = torch.zeros(nreq, dH * dd * dv + (taps - 1) * DC, device=dev)
+            dproj, second = torch.randn(n, DC + dH, device=dev), torch.randn(n, dH * dd + dH * dv, device=dev)
+            dtb, do = torch.randn(dH * dd, device=dev), torch.empty(n, dH * dv, dtype=bf, device=dev)
+            ms = timed(lambda: ops.delta_rule(ctx, dproj, second, conv_w, a_log, dtb, nw, 1e-5, dstate, dH, dG, dd, dv, taps, do))
+            kern[f"murilorn_channel_delta_rule_{label}"] = roof(ms, 0, 4.0 * (dproj.numel() + second.numel()) + 2.0 * do.numel()
+                                                                + 2 * 4.0 * dstate.numel())
+            del q, kp, vp, o, ql, pool, ol, row, proj, go, dproj, second, do
+        # feed-forwards: xIELU of one product here, SiLU-gate of two in Llama's (the dense like kernel)
+        FF = z["ff"]
+        for label, M in (("2048_tokens", T), ("8_tokens", B)):
+            h = torch.randn(M, W, device=dev).to(bf)
+            x = torch.zeros(M, W, device=dev)
+            up, dwn = (torch.randn(FF, W, device=dev) * 0.02).to(bf), (torch.randn(W, FF, device=dev) * 0.02).to(bf)
+            act = torch.empty(M, FF, dtype=bf, device=dev)
+
+            def plain():
+                ops.linear_xielu(ctx, h, up, act, 0.7, 1.2)
+                ops.linear(act, dwn, x, accumulate=True, alpha=0.5)
+
+            kern[f"xielu_feed_forward_{label}"] = roof(timed(plain), 2.0 * M * 2 * FF * W, 2.0 * 2 * FF * W)
+            g = ops.pack_gate_up((torch.randn(FF, W, device=dev) * 0.02).to(bf), (torch.randn(FF, W, device=dev) * 0.02).to(bf))
+
+            def dense():
+                ops.linear_gated(ctx, h, g, act, "silu", 0.0)
+                ops.linear(act, dwn, x, accumulate=True)
+
+            kern[f"llama_silu_feed_forward_{label}"] = roof(timed(dense), 2.0 * M * 3 * FF * W, 2.0 * 3 * FF * W)
+            del up, dwn, g, act
+        # what joins a sublayer to the residual: one pass that norms in place here; two streams written and read there
+        wv = torch.ones(W, device=dev)
+        xr, hb = torch.randn(T, W, device=dev), torch.empty(T, W, dtype=bf, device=dev)
+        kern["norm_after_the_sum_2048_tokens"] = roof(timed(lambda: ops.post_norm(xr, None, 1.0, wv, 1e-5, rounded=hb)), 0,
+                                                      (4.0 * 2 + 2.0) * T * W)
+        S = 2
+        xs, y = torch.randn(T, S, W, device=dev), torch.randn(T, W, device=dev)
+        a_in, b_out, mix = torch.ones(S, device=dev), torch.ones(S, device=dev), torch.eye(S, device=dev).contiguous()
+        on = torch.empty(T, W, dtype=bf, device=dev)
+        kern["murilorn_streams_write_and_read_2048_tokens"] = roof(
+            timed(lambda: ops.streams_update(xs, mix, b_out, y, next_in=a_in, norm_weight=wv, eps=1e-5, normed=on)), 0,
+            (8.0 * S + 4.0 + 2.0) * T * W)
+        LH, rank = z["l_heads"], z["kv_rank"]
+        mixed, gl = torch.randn(T, LH * rank, device=dev).to(bf), torch.randn(T, LH, device=dev)
+        kern["gate_per_head_2048_tokens"] = roof(timed(lambda: ops.group_gate_mul(mixed, gl, rank)), 0, 4.0 * T * LH * rank)
+        rec["kernels"] = kern
+        rec["config"] = {k: v for k, v in z.items()}
+        out["sizes"][name] = rec
+        del engines
+        torch.cuda.empty_cache()
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1119,9 +1373,9 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=0, help="context reached with --only decode (default: the shape's); keys with --only attention")
     ap.add_argument("--layers", type=int, default=0,
                     help="fewer layers than the configuration has (reported beside the full number)")
-    ap.add_argument("--design", choices=["kavenex", "murilorn", "luvapel"],
-                    help="instead of the default workload: this design beside the Llama decoder (luvapel: beside "
-                         "Murilorn, the closest of the engine's models) at equal sizes")
+    ap.add_argument("--design", choices=["kavenex", "murilorn", "luvapel", "midulorn"],
+                    help="instead of the default workload: this design beside the Llama decoder (luvapel and midulorn: "
+                         "beside Murilorn, the closest of the engine's models) at equal sizes")
     ap.add_argument("--size", default="", help="with --design: which of its sizes (2k, 4k; default both)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -1138,7 +1392,8 @@ def main() -> int:
         print("bench.py: --batch must be 1 to 64")
         return 2
     if args.design:
-        run = {"murilorn": run_design_murilorn, "luvapel": run_design_luvapel, "kavenex": run_design}[args.design]
+        run = {"murilorn": run_design_murilorn, "luvapel": run_design_luvapel, "kavenex": run_design,
+               "midulorn": run_design_midulorn}[args.design]
         print(json.dumps(run(args)))
         return 0
     print(json.dumps(run_ours(args)))
