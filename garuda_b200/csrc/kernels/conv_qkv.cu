@@ -14,7 +14,7 @@
 
 namespace {
 
-constexpr int WARPS = 4;
+constexpr int WARPS = 8;
 
 struct ConvIn {
   const float* proj;        // [T, stride]: q | k | v columns, C in all
@@ -41,8 +41,9 @@ __device__ __forceinline__ float conv_at(const ConvIn& in, const WT* __restrict_
   return y;
 }
 
-// One block per token; its warps take the heads in turn (query heads, key heads, value heads), a
-// head's channels through shared memory between the sum of squares and the store.
+// One block per token. First every thread convolves channels of its own into shared memory (all of
+// the block's loads are in flight at once); then the warps take the heads in turn (query heads, key
+// heads, value heads): the sum of squares, the scaling and the store.
 template <typename OT, typename WT>
 __global__ void __launch_bounds__(WARPS * 32)
 conv_qkv_kernel(ConvIn in, const WT* __restrict__ conv_w, OT* __restrict__ q_out, OT* __restrict__ k_pool, OT* __restrict__ v_pool,
@@ -52,10 +53,8 @@ conv_qkv_kernel(ConvIn in, const WT* __restrict__ conv_w, OT* __restrict__ q_out
                 const float* __restrict__ v_first_in, float* __restrict__ v_first_out, float lambda, int page_size) {
   gb::pdl_launch_dependents();
   gb::pdl_wait();
-  extern __shared__ float sm[];
+  extern __shared__ float sm[];            // [C]: the token's convolved row
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int widest = max(dim, vdim);
-  float* buf = sm + (size_t)warp * widest;
   const int t = blockIdx.x;
   const int r = token_req[t];
   const int i = t - cu_q[r];
@@ -63,22 +62,22 @@ conv_qkv_kernel(ConvIn in, const WT* __restrict__ conv_w, OT* __restrict__ q_out
   const int pos = positions[t];
   const int page = block_table[(size_t)r * table_width + pos / page_size];
   const int in_page = pos % page_size;
+  for (int c = threadIdx.x; c < in.C; c += WARPS * 32) sm[c] = conv_at<WT>(in, conv_w, t, i, slot, c);
+  __syncthreads();
   const int units = Hq + 2 * Hkv;
   for (int unit = warp; unit < units; unit += WARPS) {
     const bool is_q = unit < Hq, is_k = !is_q && unit < Hq + Hkv;
     const int head = is_q ? unit : is_k ? unit - Hq : unit - Hq - Hkv;
     const int width = (is_q || is_k) ? dim : vdim;
     const int col = is_q ? head * dim : is_k ? Hq * dim + head * dim : (Hq + Hkv) * dim + head * vdim;
-    float ss = 0.f;
-    for (int c = lane; c < width; c += 32) {
-      const float y = conv_at<WT>(in, conv_w, t, i, slot, col + c);
-      buf[c] = y;
-      ss += y * y;
-    }
+    float* buf = sm + col;
     const float* nw = is_q ? q_w : is_k ? k_w : nullptr;
     float inv = 1.f;
-    if (nw != nullptr) inv = 1.0f / sqrtf(gb::warp_sum(ss) / (float)width + eps);
-    __syncwarp();
+    if (nw != nullptr) {
+      float ss = 0.f;
+      for (int c = lane; c < width; c += 32) ss += buf[c] * buf[c];
+      inv = 1.0f / sqrtf(gb::warp_sum(ss) / (float)width + eps);
+    }
     if (is_q) {
       OT* o = q_out + ((size_t)t * Hq + head) * dim;
       for (int c = lane; c < width; c += 32) o[c] = gb::from_float<OT>(nw ? buf[c] * inv * nw[c] : buf[c]);
@@ -89,18 +88,14 @@ conv_qkv_kernel(ConvIn in, const WT* __restrict__ conv_w, OT* __restrict__ q_out
       }
     } else {
       const size_t at = (size_t)t * Hkv * vdim + (size_t)head * vdim;
+      OT* o = page >= 0 ? v_pool + (((size_t)page * Hkv + head) * page_size + in_page) * vdim : nullptr;
       for (int c = lane; c < width; c += 32) {
         float v = buf[c];
         if (v_first_out != nullptr) v_first_out[at + c] = v;
         if (v_first_in != nullptr) v = (1.0f - lambda) * v + lambda * v_first_in[at + c];
-        buf[c] = v;
-      }
-      if (page >= 0) {
-        OT* o = v_pool + (((size_t)page * Hkv + head) * page_size + in_page) * vdim;
-        for (int c = lane; c < width; c += 32) o[c] = gb::from_float<OT>(buf[c]);
+        if (o != nullptr) o[c] = gb::from_float<OT>(v);
       }
     }
-    __syncwarp();
   }
 }
 
@@ -150,10 +145,17 @@ GB_EXPORT int gb_conv_qkv(const float* proj, long long stride, const float* bias
   if (taps > 1 && state == nullptr) return gb::fail(GB_BAD_ARGUMENT, "conv_qkv: a convolution needs its state");
   const int C = Hq * dim + Hkv * (dim + vdim);
   const ConvIn in = {proj, stride, bias, state, state_stride, taps, C};
-  const size_t smem = (size_t)WARPS * (dim > vdim ? dim : vdim) * sizeof(float);
-  if (smem > 48 * 1024) return gb::fail(GB_UNSUPPORTED, "conv_qkv: heads of %d and %d channels", dim, vdim);
+  const size_t smem = (size_t)C * sizeof(float);
+  constexpr size_t MOST = 200 * 1024;
+  if (smem > MOST) return gb::fail(GB_UNSUPPORTED, "conv_qkv: %d projected channels (at most %d)", C, (int)(MOST / sizeof(float)));
   return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
     return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
+      static gb::OncePerDevice configured;      // (one per instance of the kernel: the lambda is instantiated per pair of types)
+      if (smem > 48 * 1024 && configured.needed()) {
+        const cudaError_t e = cudaFuncSetAttribute(conv_qkv_kernel<OT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MOST);
+        if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "conv_qkv: %s", cudaGetErrorString(e));
+        configured.done();
+      }
       return gb::check_pdl_launch(
           gb::launch_pdl(conv_qkv_kernel<OT, WT>, dim3(T), dim3(WARPS * 32), smem, stream, dim3(1, 1, 1), in, (const WT*)conv_w,
                          (OT*)q_out, (OT*)k_pool, (OT*)v_pool, positions, token_req, cu_q, slots, block_table, table_width, Hq,

@@ -87,20 +87,32 @@ post_norm_kernel(float* __restrict__ x, const float* __restrict__ y, const float
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-// grid (ceil(n / 1024), rows): a thread takes four neighbouring values of a row, one at a time
-template <typename XT>
+// grid (ceil(n / (PER * 256)), rows): a thread takes PER neighbouring values of a row. VEC: the PER
+// values are 16 bytes, lie in one group and rows start on 16 bytes, so they are one load, one gate, one store.
+template <typename XT, bool VEC>
 __global__ void __launch_bounds__(256)
 group_gate_mul_kernel(XT* __restrict__ x, const float* __restrict__ gate, int gate_stride, int n, int group) {
   gb::pdl_launch_dependents();
   gb::pdl_wait();
+  constexpr int PER = 16 / sizeof(XT);
   const size_t t = blockIdx.y;
-  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * PER;
+  if (c0 >= n) return;
   XT* xr = x + t * n;
   const float* gr = gate + t * gate_stride;
+  if (VEC) {
+    const float g = sigmoidf_(gr[c0 / group]);
+    XT v[PER];
+    *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(xr + c0);
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int c = c0 + j;
-    if (c < n) xr[c] = gb::from_float<XT>(gb::to_float<XT>(xr[c]) * sigmoidf_(gr[c / group]));
+    for (int j = 0; j < PER; ++j) v[j] = gb::from_float<XT>(gb::to_float<XT>(v[j]) * g);
+    *reinterpret_cast<uint4*>(xr + c0) = *reinterpret_cast<const uint4*>(v);
+  } else {
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int c = c0 + j;
+      if (c < n) xr[c] = gb::from_float<XT>(gb::to_float<XT>(xr[c]) * sigmoidf_(gr[c / group]));
+    }
   }
 }
 
@@ -148,10 +160,12 @@ GB_EXPORT int gb_group_gate_mul(void* x, int x_dtype, const float* gate, int gat
   if (T <= 0 || n <= 0) return GB_OK;
   if (group < 1 || n % group) return gb::fail(GB_BAD_ARGUMENT, "group_gate_mul: %d values in groups of %d", n, group);
   if (T > 65535) return gb::fail(GB_UNSUPPORTED, "group_gate_mul: %d rows (at most 65535 a call)", T);
-  const dim3 grid((n + 1023) / 1024, T);
   return GB_DISPATCH_DTYPE(x_dtype, XT, [&]() -> int {
-    return gb::check_pdl_launch(gb::launch_pdl(group_gate_mul_kernel<XT>, grid, dim3(256), 0, stream, dim3(1, 1, 1), (XT*)x, gate,
-                                               gate_stride, n, group),
+    constexpr int PER = 16 / sizeof(XT);
+    const dim3 grid((n + PER * 256 - 1) / (PER * 256), T);
+    const bool vec = group % PER == 0 && host_aligned16(x);          // (then n, a multiple of group, is one of PER too)
+    auto kernel = vec ? group_gate_mul_kernel<XT, true> : group_gate_mul_kernel<XT, false>;
+    return gb::check_pdl_launch(gb::launch_pdl(kernel, grid, dim3(256), 0, stream, dim3(1, 1, 1), (XT*)x, gate, gate_stride, n, group),
                                 "group_gate_mul");
   });
 }
