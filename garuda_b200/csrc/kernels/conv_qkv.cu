@@ -14,7 +14,7 @@
 
 namespace {
 
-constexpr int WARPS = 8;
+constexpr int WARPS = 4;
 
 struct ConvIn {
   const float* proj;        // [T, stride]: q | k | v columns, C in all
@@ -41,43 +41,103 @@ __device__ __forceinline__ float conv_at(const ConvIn& in, const WT* __restrict_
   return y;
 }
 
-// One block per token. First every thread convolves channels of its own into shared memory (all of
-// the block's loads are in flight at once); then the warps take the heads in turn (query heads, key
-// heads, value heads): the sum of squares, the scaling and the store.
-template <typename OT, typename WT>
+// The same for a number of taps known when the kernel is compiled. The rows of the step are asked
+// for before anything is known of the token's request (`row[j]` may be a row of the request in
+// front: it is then dropped for the kept row), so that these loads do not wait for the chain of
+// loads that finds the request, its slot and the token's place in it.
+template <int TAPS>
+struct Taps {
+  float row[TAPS], w[TAPS], b;
+  __device__ __forceinline__ void ask(const ConvIn& in, const float* __restrict__ conv_w, int t, int c) {
+    b = in.bias ? in.bias[c] : 0.f;
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) {
+      const int back = TAPS - 1 - j;
+      row[j] = t >= back ? in.proj[(long long)(t - back) * in.stride + c] : 0.f;
+      w[j] = conv_w[(size_t)c * TAPS + j];
+    }
+  }
+  __device__ __forceinline__ float take(const ConvIn& in, int i, int slot, int c) const {
+    float y = 0.f;
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) {
+      const int back = TAPS - 1 - j;
+      float u;
+      if (back <= i) u = row[j] + b;
+      else if (slot >= 0) u = in.state[slot * in.state_stride + (long long)(TAPS - 1 - (back - i)) * in.C + c];
+      else u = 0.f;
+      y = fmaf(w[j], u, y);
+    }
+    return y;
+  }
+};
+
+// grid (tokens, ceil(heads / WARPS)): a warp takes one head of one token (query heads, then key
+// heads, then value heads): its lanes convolve the head's channels (every load of the warp is in
+// flight at once), the sum of squares crosses the warp, the scaled values are stored. A head's
+// channels wait in shared memory between the two (a lane holds any number of them).
+// TAPS: the number of taps where it is 1 to 4 (the usual sizes), 0: any number, read from `in`.
+template <typename OT, int TAPS>
 __global__ void __launch_bounds__(WARPS * 32)
-conv_qkv_kernel(ConvIn in, const WT* __restrict__ conv_w, OT* __restrict__ q_out, OT* __restrict__ k_pool, OT* __restrict__ v_pool,
+conv_qkv_kernel(ConvIn in, const float* __restrict__ conv_w, OT* __restrict__ q_out, OT* __restrict__ k_pool, OT* __restrict__ v_pool,
                 const int32_t* __restrict__ positions, const int32_t* __restrict__ token_req, const int32_t* __restrict__ cu_q,
                 const int32_t* __restrict__ slots, const int32_t* __restrict__ block_table, int table_width, int Hq, int Hkv,
                 int dim, int vdim, const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
                 const float* __restrict__ v_first_in, float* __restrict__ v_first_out, float lambda, int page_size) {
   gb::pdl_launch_dependents();
   gb::pdl_wait();
-  extern __shared__ float sm[];            // [C]: the token's convolved row
+  extern __shared__ float sm[];            // [WARPS][max(dim, vdim)]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int unit = blockIdx.y * WARPS + warp;
+  if (unit >= Hq + 2 * Hkv) return;
   const int t = blockIdx.x;
+  const bool is_q = unit < Hq, is_k = !is_q && unit < Hq + Hkv;
+  const int head = is_q ? unit : is_k ? unit - Hq : unit - Hq - Hkv;
+  const int width = (is_q || is_k) ? dim : vdim;
+  const int col = is_q ? head * dim : is_k ? Hq * dim + head * dim : (Hq + Hkv) * dim + head * vdim;
+  constexpr int N = TAPS > 0 ? TAPS : 1;
+  constexpr int FIRST = 4;                  // channels of a lane whose rows are asked for ahead of everything else
+  Taps<N> ahead[FIRST];
+  if (TAPS > 0) {
+#pragma unroll
+    for (int k = 0; k < FIRST; ++k)
+      if (lane + 32 * k < width) ahead[k].ask(in, conv_w, t, col + lane + 32 * k);
+  }
   const int r = token_req[t];
   const int i = t - cu_q[r];
   const int slot = slots[r];
   const int pos = positions[t];
   const int page = block_table[(size_t)r * table_width + pos / page_size];
   const int in_page = pos % page_size;
-  for (int c = threadIdx.x; c < in.C; c += WARPS * 32) sm[c] = conv_at<WT>(in, conv_w, t, i, slot, c);
-  __syncthreads();
-  const int units = Hq + 2 * Hkv;
-  for (int unit = warp; unit < units; unit += WARPS) {
-    const bool is_q = unit < Hq, is_k = !is_q && unit < Hq + Hkv;
-    const int head = is_q ? unit : is_k ? unit - Hq : unit - Hq - Hkv;
-    const int width = (is_q || is_k) ? dim : vdim;
-    const int col = is_q ? head * dim : is_k ? Hq * dim + head * dim : (Hq + Hkv) * dim + head * vdim;
-    float* buf = sm + col;
-    const float* nw = is_q ? q_w : is_k ? k_w : nullptr;
-    float inv = 1.f;
-    if (nw != nullptr) {
-      float ss = 0.f;
-      for (int c = lane; c < width; c += 32) ss += buf[c] * buf[c];
-      inv = 1.0f / sqrtf(gb::warp_sum(ss) / (float)width + eps);
+  {
+    float* buf = sm + (size_t)warp * max(dim, vdim);
+    float ss = 0.f;
+    if (TAPS > 0) {
+#pragma unroll
+      for (int k = 0; k < FIRST; ++k) {
+        const int c = lane + 32 * k;
+        if (c < width) {
+          const float y = ahead[k].take(in, i, slot, col + c);
+          buf[c] = y;                        // (read back by the lane that wrote it)
+          ss += y * y;
+        }
+      }
+      for (int c = lane + 32 * FIRST; c < width; c += 32) {
+        Taps<N> one;
+        one.ask(in, conv_w, t, col + c);
+        const float y = one.take(in, i, slot, col + c);
+        buf[c] = y;
+        ss += y * y;
+      }
+    } else {
+      for (int c = lane; c < width; c += 32) {
+        const float y = conv_at<float>(in, conv_w, t, i, slot, col + c);
+        buf[c] = y;
+        ss += y * y;
+      }
     }
+    const float* nw = is_q ? q_w : is_k ? k_w : nullptr;
+    const float inv = nw != nullptr ? 1.0f / sqrtf(gb::warp_sum(ss) / (float)width + eps) : 1.f;
     if (is_q) {
       OT* o = q_out + ((size_t)t * Hq + head) * dim;
       for (int c = lane; c < width; c += 32) o[c] = gb::from_float<OT>(nw ? buf[c] * inv * nw[c] : buf[c]);
@@ -145,23 +205,19 @@ GB_EXPORT int gb_conv_qkv(const float* proj, long long stride, const float* bias
   if (taps > 1 && state == nullptr) return gb::fail(GB_BAD_ARGUMENT, "conv_qkv: a convolution needs its state");
   const int C = Hq * dim + Hkv * (dim + vdim);
   const ConvIn in = {proj, stride, bias, state, state_stride, taps, C};
-  const size_t smem = (size_t)C * sizeof(float);
-  constexpr size_t MOST = 200 * 1024;
-  if (smem > MOST) return gb::fail(GB_UNSUPPORTED, "conv_qkv: %d projected channels (at most %d)", C, (int)(MOST / sizeof(float)));
+  const size_t smem = (size_t)WARPS * (dim > vdim ? dim : vdim) * sizeof(float);
+  if (smem > 48 * 1024) return gb::fail(GB_UNSUPPORTED, "conv_qkv: heads of %d and %d channels", dim, vdim);
+  const int units = Hq + 2 * Hkv;
+  if ((units + WARPS - 1) / WARPS > 65535) return gb::fail(GB_UNSUPPORTED, "conv_qkv: %d heads", units);
+  if (w_dtype != GB_F32) return gb::fail(GB_BAD_ARGUMENT, "conv_qkv: the taps are 32-bit");
   return GB_DISPATCH_DTYPE(out_dtype, OT, [&]() -> int {
-    return GB_DISPATCH_DTYPE(w_dtype, WT, [&]() -> int {
-      static gb::OncePerDevice configured;      // (one per instance of the kernel: the lambda is instantiated per pair of types)
-      if (smem > 48 * 1024 && configured.needed()) {
-        const cudaError_t e = cudaFuncSetAttribute(conv_qkv_kernel<OT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MOST);
-        if (e != cudaSuccess) return gb::fail(GB_CUDA_ERROR, "conv_qkv: %s", cudaGetErrorString(e));
-        configured.done();
-      }
-      return gb::check_pdl_launch(
-          gb::launch_pdl(conv_qkv_kernel<OT, WT>, dim3(T), dim3(WARPS * 32), smem, stream, dim3(1, 1, 1), in, (const WT*)conv_w,
-                         (OT*)q_out, (OT*)k_pool, (OT*)v_pool, positions, token_req, cu_q, slots, block_table, table_width, Hq,
-                         Hkv, dim, vdim, q_w, k_w, eps, v_first_in, v_first_out, lambda, page_size),
-          "conv_qkv");
-    });
+    auto kernel = taps == 1 ? conv_qkv_kernel<OT, 1> : taps == 2 ? conv_qkv_kernel<OT, 2> : taps == 3 ? conv_qkv_kernel<OT, 3>
+                : taps == 4 ? conv_qkv_kernel<OT, 4> : conv_qkv_kernel<OT, 0>;
+    return gb::check_pdl_launch(
+        gb::launch_pdl(kernel, dim3(T, (units + WARPS - 1) / WARPS), dim3(WARPS * 32), smem, stream, dim3(1, 1, 1), in,
+                       (const float*)conv_w, (OT*)q_out, (OT*)k_pool, (OT*)v_pool, positions, token_req, cu_q, slots, block_table,
+                       table_width, Hq, Hkv, dim, vdim, q_w, k_w, eps, v_first_in, v_first_out, lambda, page_size),
+        "conv_qkv");
   });
 }
 

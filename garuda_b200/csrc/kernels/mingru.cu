@@ -42,10 +42,32 @@ __device__ __forceinline__ void gates(const Rows& in, long long t, int c, float 
   b = z * n;
 }
 
-// Walks tokens [t0, t1) of channel c from S, writing the gated read-out; returns the last S.
+constexpr int AHEAD = 8;      // tokens whose rows a thread asks for before it needs the first of them
+
+// Walks tokens [t0, t1) of channel c from S, writing the gated read-out; returns the last S. The
+// rows of AHEAD tokens are loaded before the chain of multiply-adds over them runs: what bounds a
+// walk is the loads' latency, and nothing in a load depends on S.
 template <typename OT>
 __device__ __forceinline__ float walk(const Rows& in, int t0, int t1, int c, float bz, float bu, float S, OT* out, int W) {
-  for (int t = t0; t < t1; ++t) {
+  int t = t0;
+  for (; t + AHEAD <= t1; t += AHEAD) {
+    float a[AHEAD], u[AHEAD], g[AHEAD];
+#pragma unroll
+    for (int k = 0; k < AHEAD; ++k) {
+      const float* row = in.proj + (long long)(t + k) * in.stride;
+      a[k] = row[in.z_col + c];
+      u[k] = row[in.u_col + c];
+      g[k] = row[in.g_col + c];
+    }
+#pragma unroll
+    for (int k = 0; k < AHEAD; ++k) {
+      const float z = sigmoidf_(a[k] + bz), v = u[k] + bu;
+      const float n = v >= 0.f ? v + 0.5f : sigmoidf_(v);
+      S = fmaf(1.0f - z, S, z * n);
+      out[(size_t)(t + k) * W + c] = gb::from_float<OT>(S * (g[k] * sigmoidf_(g[k])));
+    }
+  }
+  for (; t < t1; ++t) {
     float p, b;
     gates(in, t, c, bz, bu, p, b);
     S = fmaf(p, S, b);
@@ -94,7 +116,24 @@ mingru_parts_kernel(Rows in, const int32_t* __restrict__ cu_q, const int32_t* __
   const int t1 = min(end, t0 + SEG);
   const float bz = in.bz ? in.bz[c] : 0.f, bu = in.bu ? in.bu[c] : 0.f;
   float P = 1.f, B = 0.f;
-  for (int t = t0; t < t1; ++t) {
+  int t = t0;
+  for (; t + AHEAD <= t1; t += AHEAD) {
+    float a[AHEAD], u[AHEAD];
+#pragma unroll
+    for (int k = 0; k < AHEAD; ++k) {
+      const float* row = in.proj + (long long)(t + k) * in.stride;
+      a[k] = row[in.z_col + c];
+      u[k] = row[in.u_col + c];
+    }
+#pragma unroll
+    for (int k = 0; k < AHEAD; ++k) {
+      const float z = sigmoidf_(a[k] + bz), v = u[k] + bu;
+      const float n = v >= 0.f ? v + 0.5f : sigmoidf_(v);
+      P *= 1.0f - z;
+      B = fmaf(1.0f - z, B, z * n);
+    }
+  }
+  for (; t < t1; ++t) {
     float p, b;
     gates(in, t, c, bz, bu, p, b);
     P *= p;
