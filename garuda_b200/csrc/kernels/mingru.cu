@@ -1,4 +1,4 @@
-// A gated recurrence whose gates read only the current token (minGRU), per channel c:
+// minGRU: a recurrence per channel c whose gate and candidate are functions of the current token alone:
 //
 //   z_t = sigmoid(a_t + bz)          a, u, g: three column ranges of one projected 32-bit row
 //   n_t = u_t + bu + 1/2  where u_t + bu >= 0,  sigmoid(u_t + bu)  below

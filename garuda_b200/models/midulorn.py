@@ -7,7 +7,7 @@ but a term that grows with the logarithm of the distance, a mask of fixed stretc
 positions, a learned sink per head, biases on its four projections, and values that are mixed
 with those of the first such layer; attention over a cached latent with one rotated key part
 for all heads (pairs ``(i, i + dims / 2)``), a learned sink per head and a gate per head; or a
-gated recurrence per channel whose gates read only the current token. The feed-forward is
+recurrence per channel whose gate and candidate are functions of the current token alone. The feed-forward is
 ``down(xielu(up h))`` or routed experts weighed by their share of a softmax over all experts,
 or absent. A final norm; the head is the embedding table, the logits times a constant.
 Tensor names: ``embed``, ``final.norm``, and per layer ``l<i>.norm1|norm2``, ``l<i>.mix.*``,

@@ -1,4 +1,4 @@
-"""A gated recurrence whose gates read only the current token (minGRU).
+"""minGRU: a recurrence per channel whose gate and candidate are functions of the current token alone.
 
 With ``x`` the mixer's input and one state ``S`` of ``inner`` channels per request:
 

@@ -86,7 +86,7 @@ def batches(b):
 
 
 # ---------------------------------------------------------------------------- kernels
-@pytest.mark.parametrize("T,d", [(1, 40), (37, 192), (5, 1030), (3, 4096)])
+@pytest.mark.parametrize("T,d", [(1, 40), (37, 200), (5, 1030), (3, 4096)])
 def test_norm_after_the_sum_in_one_pass(both, T, d):
     ops, ref, dt = both
     x, y, row, w = rnd(T, d, seed=1), rnd(T, d, seed=2), rnd(d, seed=3), rnd(d, seed=4)
@@ -126,7 +126,7 @@ def test_a_gate_per_head(both, T, H, group):
     close(got, want, dt, "group_gate_mul")
 
 
-@pytest.mark.parametrize("M,N,K", [(21, 77, 40), (3, 384, 192), (300, 1024, 256), (2048, 512, 128)])
+@pytest.mark.parametrize("M,N,K", [(21, 77, 40), (3, 320, 160), (300, 1024, 256), (2048, 512, 128)])
 def test_xielu_behind_a_product(both, M, N, K):
     ops, ref, dt = both
     a, w = rnd(M, K, dtype=dt, seed=1), rnd(N, K, dtype=dt, scale=0.3, seed=2)
@@ -213,8 +213,8 @@ def test_convolved_projections_into_pages(both, taps, H, G, dim, vdim):
         close(vog, vo, torch.float32, "the values handed on")
 
 
-@pytest.mark.parametrize("H,G,dim,vdim,ps", [(6, 2, 24, 40, 8), (4, 1, 64, 64, 32), (8, 2, 32, 64, 16), (2, 2, 128, 128, 64)])
-@pytest.mark.parametrize("chunk", [0, 7, 16, 33, 96])
+@pytest.mark.parametrize("H,G,dim,vdim,ps", [(6, 2, 24, 40, 8), (4, 2, 64, 64, 32), (8, 2, 32, 64, 16), (2, 2, 128, 128, 64)])
+@pytest.mark.parametrize("chunk", [0, 7, 16, 33, 80])
 def test_attention_with_sinks_distance_and_stretches(both, H, G, dim, vdim, ps, chunk):
     """Mixed steps over pages drawn at random; stretches that end inside a page, at its border and
     beyond the step's first token. One key far back is made to stand out (its row and the queries
@@ -245,7 +245,7 @@ def test_attention_with_sinks_distance_and_stretches(both, H, G, dim, vdim, ps, 
         assert (other[T - 1, :vdim].float() - want[T - 1, :vdim].float()).abs().max() > 0.05
 
 
-@pytest.mark.parametrize("H,rank,rot,ps", [(3, 20, 6, 8), (8, 128, 16, 32), (4, 64, 16, 16), (2, 128, 32, 64)])
+@pytest.mark.parametrize("H,rank,rot,ps", [(3, 20, 6, 8), (8, 96, 16, 32), (4, 64, 16, 16), (2, 128, 32, 64)])
 def test_attention_over_latent_rows_with_sinks(both, H, rank, rot, ps):
     ops, ref, dt = both
     lens, starts = [5, 1, 70, 2, 1], [0, 37, 13, 190, 500]
@@ -267,7 +267,7 @@ def test_attention_over_latent_rows_with_sinks(both, H, rank, rot, ps):
     close(got, want, dt, "latent attention with sinks", 3e-2 if dt == torch.bfloat16 else 2e-5)
 
 
-@pytest.mark.parametrize("T,E,K,top", [(19, 11, 48, 3), (1, 4, 200, 4), (300, 64, 128, 1), (7, 12, 192, 4)])
+@pytest.mark.parametrize("T,E,K,top", [(19, 11, 48, 3), (1, 4, 200, 4), (300, 64, 128, 1), (7, 10, 176, 3)])
 def test_router_over_all_experts(both, T, E, K, top):
     ops, ref, dt = both
     h, w = rnd(T, K, dtype=dt, seed=1), rnd(E, K, dtype=dt, scale=0.5, seed=2)
