@@ -60,6 +60,8 @@ def midulorn_spec(cfg: MidulornConfig) -> ModelSpec:
         ff = _feed_forward(cfg, layer.mlp, p + "mlp.")
         if ff is None:
             ignored.append(p + "norm2")
+        if layer.type == "attention" and not layer.mixer.v_mix:
+            ignored.append(p + "mix.vmix")           # (a folder may carry the mixing weight of a layer that mixes nothing)
         layers.append(BlockSpec(mixer=_mixer(cfg, layer, p + "mix.", first_mixed), feed_forward=ff,
                                 mixer_norm=_norm(cfg, p, "norm1"),
                                 feed_forward_norm=_norm(cfg, p, "norm2") if ff is not None else None,
