@@ -180,3 +180,34 @@ def test_kept_first_positions_hold_their_pages_while_the_window_moves_on():
     m.check_invariants()
     with pytest.raises(host.CacheError):
         host.CacheManager([host.GroupConfig(4, 6, -1)], 4, 2, 64)
+
+
+def test_a_chunked_group_gives_back_the_stretches_in_front():
+    # pages of 4, stretches of 6 positions: a query at position n reads from floor(n / 6) * 6 on
+    m = host.CacheManager([host.GroupConfig(8, 0, 0, 6), host.GroupConfig(16)], 4, 2, 64)
+    m.acquire(1)
+    for n in range(1, 31):
+        m.reserve(1, n)
+        m.commit(1, n)
+        m.check_invariants()
+        assert m.first_live_position(0, n) == n // 6 * 6 and m.first_live_position(1, n) == 0
+        chunked, plain = list(m.block_table_row(1, 0)), list(m.block_table_row(1, 1))
+        first = (n // 6 * 6) // 4                 # the page that holds the next query's first key
+        last = (n + 3) // 4
+        assert all(chunked[p] < 0 for p in range(first)) and all(chunked[p] >= 0 for p in range(first, last))
+        assert all(plain[p] >= 0 for p in range(last))
+        assert m.free_pages(0) >= 8 - 3           # a stretch of 6 touches at most three pages of 4
+    # a portion that crosses a stretch's border is backed whole until it is committed
+    m.acquire(2)
+    m.reserve(2, 15)
+    assert [p >= 0 for p in m.block_table_row(2, 0)[:4]] == [True, True, True, True]
+    m.commit(2, 15)
+    assert [p >= 0 for p in m.block_table_row(2, 0)[:4]] == [False, False, False, True]
+    m.check_invariants()
+    m.release(1)
+    m.release(2)
+    assert m.free_pages(0) == 8 and m.pages_reused > 0
+    with pytest.raises(host.CacheError):
+        host.CacheManager([host.GroupConfig(4, 6, 0, 5)], 4, 2, 64)      # a window and a chunk at once
+    with pytest.raises(host.CacheError):
+        host.CacheManager([host.GroupConfig(4, 0, 0, -1)], 4, 2, 64)
